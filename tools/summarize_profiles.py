@@ -28,7 +28,7 @@ def full_report(rep, out_md, title):
             "sm__inst_executed_pipe_tensor.sum", "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active", "lts__t_sector_hit_rate.pct"]
     idx = [hdr.index(w) for w in want if w in hdr]
     with open(out_md, "w") as f:
-        f.write(f"# {title}\n\nSource: `{os.path.relpath(rep, ROOT)}` (`ncu --set full --clock-control none --import-source on`), one row per captured launch.\n\n")
+        f.write(f"# {title}\n\nSource: `{os.path.relpath(rep, ROOT)}` (`ncu --set full --clock-control none`), one row per captured launch.\n\n")
         f.write("| " + " | ".join(f"{hdr[i]} ({units[i]})" if units[i] else hdr[i] for i in idx) + " |\n|" + "---|" * len(idx) + "\n")
         for row in r[2:]:
             f.write("| " + " | ".join(row[i][:70] for i in idx) + " |\n")
@@ -111,7 +111,7 @@ def full_report_wide(rep, out_md, title, note=""):
     stalls = [h for h in hdr if h.startswith("smsp__average_warps_issue_stalled_") and h.endswith("_per_issue_active.ratio") and "not_issued" not in h]
     idx = [hdr.index(w) for w in want if w in hdr]
     with open(out_md, "w") as f:
-        f.write(f"# {title}\n\nSource: `{os.path.relpath(rep, ROOT)}` (`ncu --set full --clock-control none --import-source on`), one block per captured launch."
+        f.write(f"# {title}\n\nSource: `{os.path.relpath(rep, ROOT)}` (`ncu --set full --clock-control none`), one block per captured launch."
                 f"  Numbers taken under the profiler are never bench values.\n\n{note}\n")
         for row in r[2:]:
             f.write(f"\n## `{row[hdr.index('Kernel Name')][:100]}`\n\n| metric | value |\n|---|---|\n")
