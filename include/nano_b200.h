@@ -45,6 +45,8 @@ extern "C" {
 #define NB200_FLAG_EXACT 0x1u      /* exact mode: reference-order fp32 reductions (validation, slower) */
 #define NB200_FLAG_NO_GRAPH 0x2u   /* launch kernels directly instead of replaying a CUDA graph */
 #define NB200_FLAG_NO_PDL 0x4u     /* disable programmatic dependent launch */
+#define NB200_FLAG_F32 0x20u       /* model folders: true 32-bit compute (weights widened to fp32, fp32 FMA matrix products, no tensor-core rounding);
+                                      the default keeps the file's bfloat16 weights and feeds the tensor cores bfloat16 operands with fp32 accumulation */
 #define NB200_FLAG_NO_STREAM 0x10u /* do not use the grid-wide streaming kernel (per-CTA TMA weight ring, one launch per run of tokens) */
 
 /* quantisation / architecture ids: identical to infer/tensor.h:72-76 and infer/infer.h:45-47 */
@@ -54,6 +56,7 @@ extern "C" {
 #define NB200_ARCH_NANO 0u
 #define NB200_ARCH_QWEN2 2u
 #define NB200_ARCH_QWEN3 3u
+#define NB200_ARCH_LAYERED 16u     /* a model folder whose config.json lists typed layers (nb200_engine_create_dir) */
 
 typedef struct nb200_engine nb200_engine;
 
@@ -117,6 +120,26 @@ int nb200_lora_enable(nb200_engine *e, int on);
 int nb200_lora_unload(nb200_engine *e);
 
 int nb200_get_config(const nb200_engine *e, nb200_config *cfg);
+
+/* ---- model folders and sequences (the reference has no counterpart: its engine reads one file format and holds one session) ----
+ * nb200_engine_create_dir loads `model_dir`/config.json and `model_dir`/model.safetensors; config "architecture" picks the model
+ * family from the library's registry (csrc/api.cu).  `max_tokens` is the number of tokens all live sequences may hold together; it
+ * sizes the paged cache.  Such an engine also answers nb200_forward / next_greedy / next_sampled / decode_greedy / read_logits
+ * (they drive one implicit sequence, positions must arrive in order, pos 0 starts over), so the generation hosts work unchanged.
+ *
+ * A sequence owns cache pages and one recurrent-state slot.  nb200_step runs the `n` next tokens of `seq` from the state earlier
+ * steps left (n > 1: the prefill kernels; n == 1: the decode kernels) and copies the logits at the `n_want` places want[] (indices
+ * into this step's tokens, ascending) to `logits` [n_want][vocab].  nb200_seq_close gives pages and slot back. */
+int nb200_engine_create_dir(nb200_engine **out, const char *model_dir, uint32_t max_tokens, int device, uint32_t flags);
+int nb200_seq_open(nb200_engine *e, uint32_t *seq);
+int nb200_seq_close(nb200_engine *e, uint32_t seq);
+int nb200_step(nb200_engine *e, uint32_t seq, const uint32_t *tokens, uint32_t n, const uint32_t *want, uint32_t n_want, float *logits);
+/* the same step `reps` times from the same state (state and cache are restored in between), timed with CUDA events on the engine's
+ * stream after one untimed run: ms[0] = mean milliseconds of one run.  For bench.py. */
+int nb200_step_timed(nb200_engine *e, uint32_t seq, const uint32_t *tokens, uint32_t n, uint32_t reps, float *ms);
+/* parity tests: the residual stream after layer run `run` of the last step, [tokens of that step][width] (engine created with
+ * NB200_KEEP_RESIDUALS=1 in the environment) */
+int nb200_read_residual(nb200_engine *e, uint32_t run, float *dst, uint32_t count);
 
 /* one token through the network; logits stay in HBM.  is_causal=0 is the reference's seq2seq mode
  * (attention over all max_seq_len cache rows, infer.c:849). */

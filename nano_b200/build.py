@@ -37,20 +37,33 @@ def _newer(target: str, sources) -> bool:
 
 # translation units of libnano_b200.so and what each depends on (besides itself)
 UNITS = {
-    "engine.cu": ["kernels.cuh", "expf_ref.cuh", "stream_args.h", "stream_host.h", "sample_host.h", "../../include/nano_b200.h"],
+    "api.cu": ["family.h", "modeldir.h", "../../include/nano_b200.h"],
+    "modeldir.cu": ["modeldir.h"],
+    "layered.cu": ["layered_kernels.cuh", "family.h", "modeldir.h", "sample_host.h", "../../include/nano_b200.h"],
+    "engine.cu": ["kernels.cuh", "expf_ref.cuh", "stream_args.h", "stream_host.h", "sample_host.h", "family.h", "../../include/nano_b200.h"],
     "stream.cu": ["kernels.cuh", "expf_ref.cuh", "stream_args.h", "stream_host.h", "stream.cuh"],
     "sample.cu": ["kernels.cuh", "expf_ref.cuh", "sample_host.h"],
 }
 
 
-def build_engine(force: bool = False, verbose: bool = False) -> str:
-    """One object per translation unit (compiled in parallel, only when its sources changed), then one link."""
+# the units a model FOLDER (config.json + model.safetensors) needs: registry, folder reader, layered runtime, device sampler.
+# The model-file family (engine.cu, stream.cu: minutes of nvcc) is not among them.
+LAYERED_UNITS = ["api.cu", "modeldir.cu", "layered.cu", "sample.cu"]
+LAYERED_SO = os.path.join(LIB, "libnano_b200_layered.so")
+
+
+def build_engine(force: bool = False, verbose: bool = False, units=None, target: str = None) -> str:
+    """One object per translation unit (compiled in parallel, only when its sources changed), then one link.
+    units / target: a library of a subset of the families (build_layered)."""
     os.makedirs(LIB, exist_ok=True)
+    target = target or ENGINE_SO
     base = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
     if verbose:
         base.insert(1, "-Xptxas=-v")
     objs, procs = [], []
     for unit, deps in UNITS.items():
+        if units is not None and unit not in units:
+            continue
         obj = os.path.join(LIB, unit[:-3] + ".o")
         objs.append(obj)
         if force or _newer(obj, [os.path.join(CSRC, unit)] + [os.path.join(CSRC, d) for d in deps]):
@@ -58,9 +71,17 @@ def build_engine(force: bool = False, verbose: bool = False) -> str:
     failed = [u for u, p in procs if p.wait() != 0]
     if failed:
         raise RuntimeError("nvcc failed for " + ", ".join(failed))
-    if procs or _newer(ENGINE_SO, objs):
-        subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", ENGINE_SO] + objs, check=True)
-    return ENGINE_SO
+    if procs or _newer(target, objs):
+        tmp = target + ".%d.tmp" % os.getpid()          # another process may be building the same library: link aside, then rename
+        subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp] + objs, check=True)
+        os.replace(tmp, target)
+    return target
+
+
+def build_layered(force: bool = False) -> str:
+    """libnano_b200_layered.so: the same C-ABI with only the model-folder families linked in (seconds to build).  A host that serves
+    such a model in a fresh checkout builds this; the full library answers the same calls once it exists."""
+    return build_engine(force, units=LAYERED_UNITS, target=LAYERED_SO)
 
 
 TRACE_SO = os.path.join(LIB, "libnano_b200_trace.so")

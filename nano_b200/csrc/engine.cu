@@ -29,29 +29,15 @@
 #include "kernels.cuh"
 #include "stream_host.h"
 #include "sample_host.h"
+#include "family.h"
 
 using namespace nb;
 
 namespace {
 
-thread_local std::string g_err;
+using nb::fail;
 
-int fail(int code, const char *fmt, ...) {
-    char buf[512];
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(buf, sizeof buf, fmt, ap);
-    va_end(ap);
-    g_err = buf;
-    return code;
-}
-
-#define CK(call)                                                                                     \
-    do {                                                                                             \
-        cudaError_t e_ = (call);                                                                     \
-        if (e_ != cudaSuccess)                                                                       \
-            return fail(NB200_ECUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
-    } while (0)
+#define CK(call) NB_CK(call)
 
 inline uint32_t rd_u32(const uint8_t *p) { uint32_t v; memcpy(&v, p, 4); return v; }
 inline uint64_t rd_u64(const uint8_t *p) { uint64_t v; memcpy(&v, p, 8); return v; }
@@ -78,7 +64,11 @@ __global__ void k_q4k_split(const uint8_t *__restrict__ blocks, uint64_t nblocks
 
 }  // namespace
 
-struct nb200_engine {
+extern "C" const nb::EngineOps kNanoOps;
+// entry points that exist for this family only refuse the engines of another one (their handle is a different object)
+#define NANO_ONLY(e) do { if ((e) && (e)->ops != &kNanoOps) return nb::fail(NB200_EINVAL, "%s serves model-file (Nano family) engines only", __func__); } while (0)
+
+struct nb200_engine : nb::EngineBase {
     Dims d{};
     uint32_t flags = 0;
     int device = 0, num_sms = 148;
@@ -109,8 +99,6 @@ struct nb200_engine {
     void *samp_ws = nullptr; size_t samp_cub = 0; uint32_t *samp_host = nullptr;       // device-side sampler workspace (sample.cu), pinned result
     uint64_t stream_bytes = 0;
     unsigned int *bar = nullptr;
-    uint64_t launches = 0, weight_bytes = 0;
-    uint32_t launches_per_token = 0;
     std::vector<uint32_t> seen_mirror;   // ids whose seen[] flag is set, by position
     bool seen_valid = false;
     std::vector<void *> allocs;
@@ -640,15 +628,7 @@ int setup_stream(nb200_engine *e) {
 // =================================================================================================
 extern "C" {
 
-const char *nb200_last_error(void) { return g_err.c_str(); }
-
-int nb200_device_count(void) {
-    int n = 0;
-    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
-    return n;
-}
-
-void nb200_engine_destroy(nb200_engine *e) {
+static void nano_destroy(nb200_engine *e) {
     if (!e) return;
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
@@ -680,7 +660,8 @@ static int create_impl(nb200_engine **out, const uint8_t *img, uint64_t image_by
         if (ex && atoi(ex) != 0) flags |= NB200_FLAG_EXACT;
     }
     nb200_engine *e = new nb200_engine();
-    struct Guard { nb200_engine *e; bool ok = false; ~Guard() { if (!ok) nb200_engine_destroy(e); } } guard{e};
+    e->ops = &kNanoOps;
+    struct Guard { nb200_engine *e; bool ok = false; ~Guard() { if (!ok) nano_destroy(e); } } guard{e};
     e->device = device; e->flags = flags; e->tp_rank = tp_rank; e->tp_size = tp_size;
     e->use_pdl = !(flags & NB200_FLAG_NO_PDL);
     cudaDeviceProp prop;
@@ -995,7 +976,7 @@ static int calibrate_paths(nb200_engine *e) {
     return 0;
 }
 
-int nb200_engine_create(nb200_engine **out, const uint8_t *img, uint64_t image_bytes, uint32_t max_seq_len, int device,
+int nb_family_nano_create(nb200_engine **out, const uint8_t *img, uint64_t image_bytes, uint32_t max_seq_len, int device,
                         uint32_t flags) {
     return create_impl(out, img, image_bytes, max_seq_len, device, flags, 0, 1);
 }
@@ -1020,6 +1001,7 @@ static int lora_set_active(nb200_engine *e, bool on) {
 /* nb200_lora_load <- load_lora_from_buffer infer/infer.c:513-519 (parse_lora_file :436-500, malloc_fwd_buffer_with_lora :413-433).
  * image_bytes == 0: trust the header like the reference does. */
 int nb200_lora_load(nb200_engine *e, const uint8_t *img, uint64_t image_bytes) {
+    NANO_ONLY(e);
     if (!e || !img) return fail(NB200_EINVAL, "null argument");
     if (e->tp_size > 1) return fail(NB200_EINVAL, "LoRA is not available on tensor-parallel engines");
     if (e->lora.loaded) return fail(NB200_EINVAL, "a LoRA plug-in is already loaded");
@@ -1048,6 +1030,7 @@ int nb200_lora_load(nb200_engine *e, const uint8_t *img, uint64_t image_bytes) {
 
 /* use_lora of llm_forward (infer.c:713, 792, 898): run with (1) or without (0) the loaded plug-in */
 int nb200_lora_enable(nb200_engine *e, int on) {
+    NANO_ONLY(e);
     if (!e) return fail(NB200_EINVAL, "null engine");
     if (!e->lora.loaded) return on ? fail(NB200_EINVAL, "no LoRA plug-in loaded") : 0;
     return lora_set_active(e, on != 0);
@@ -1055,6 +1038,7 @@ int nb200_lora_enable(nb200_engine *e, int on) {
 
 /* nb200_lora_unload <- free_lora infer/infer.c:521-534 */
 int nb200_lora_unload(nb200_engine *e) {
+    NANO_ONLY(e);
     if (!e) return fail(NB200_EINVAL, "null engine");
     if (!e->lora.loaded) return 0;
     int r = lora_set_active(e, false);
@@ -1070,6 +1054,7 @@ int nb200_lora_unload(nb200_engine *e) {
 }
 
 int nb200_tp_export(nb200_engine *e, void *handle64) {
+    NANO_ONLY(e);
     if (!e || !handle64 || e->tp_size <= 1) return fail(NB200_EINVAL, "not a tensor-parallel engine");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
     CK(cudaSetDevice(e->device));
@@ -1085,6 +1070,7 @@ static int tp_finish_attach(nb200_engine *e) {
 }
 
 int nb200_tp_attach_ipc(nb200_engine *e, const void *handles) {
+    NANO_ONLY(e);
     if (!e || !handles || e->tp_size <= 1) return fail(NB200_EINVAL, "not a tensor-parallel engine");
     if (e->tp_attached) return fail(NB200_EINVAL, "already attached");
     CK(cudaSetDevice(e->device));
@@ -1102,6 +1088,7 @@ int nb200_tp_attach_ipc(nb200_engine *e, const void *handles) {
 }
 
 int nb200_tp_attach_local(nb200_engine *e, nb200_engine *const *group) {
+    NANO_ONLY(e);
     if (!e || !group || e->tp_size <= 1) return fail(NB200_EINVAL, "not a tensor-parallel engine");
     if (e->tp_attached) return fail(NB200_EINVAL, "already attached");
     CK(cudaSetDevice(e->device));
@@ -1122,7 +1109,7 @@ int nb200_tp_attach_local(nb200_engine *e, nb200_engine *const *group) {
     return tp_finish_attach(e);
 }
 
-int nb200_get_config(const nb200_engine *e, nb200_config *c) {
+static int nano_get_config(const nb200_engine *e, nb200_config *c) {
     if (!e || !c) return fail(NB200_EINVAL, "null argument");
     memset(c, 0, sizeof *c);
     const Dims &d = e->d;
@@ -1156,7 +1143,7 @@ static int push_state(nb200_engine *e, uint32_t pos, uint32_t causal, uint32_t n
     return 0;
 }
 
-int nb200_forward(nb200_engine *e, uint32_t token, uint32_t pos, uint32_t is_causal) {
+static int nano_forward(nb200_engine *e, uint32_t token, uint32_t pos, uint32_t is_causal) {
     if (!e) return fail(NB200_EINVAL, "null engine");
     if (pos >= e->d.max_seq || token >= e->d.V) return fail(NB200_EINVAL, "token/pos out of range");
     CK(cudaSetDevice(e->device));
@@ -1167,7 +1154,7 @@ int nb200_forward(nb200_engine *e, uint32_t token, uint32_t pos, uint32_t is_cau
     return tp_check(e);
 }
 
-int nb200_read_logits(nb200_engine *e, float *host_logits) {
+static int nano_read_logits(nb200_engine *e, float *host_logits) {
     if (!e || !host_logits) return fail(NB200_EINVAL, "null argument");
     CK(cudaSetDevice(e->device));
     CK(cudaMemcpyAsync(host_logits, e->logits, (size_t)e->d.V * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -1193,7 +1180,7 @@ static int sync_seen(nb200_engine *e, const uint32_t *ids, uint32_t pos) {
     return 0;
 }
 
-int nb200_next_greedy(nb200_engine *e, const uint32_t *ids, uint32_t pos, int is_prefilling, float penalty, uint32_t *next) {
+static int nano_next_greedy(nb200_engine *e, const uint32_t *ids, uint32_t pos, int is_prefilling, float penalty, uint32_t *next) {
     if (!e || !ids || !next) return fail(NB200_EINVAL, "null argument");
     if (pos >= e->d.max_seq || ids[pos] >= e->d.V) return fail(NB200_EINVAL, "token/pos out of range");
     CK(cudaSetDevice(e->device));
@@ -1209,7 +1196,7 @@ int nb200_next_greedy(nb200_engine *e, const uint32_t *ids, uint32_t pos, int is
 
 /* nb200_next_sampled <- generate_next_token, temperature > 0 branch (infer.c:1156-1189: penalty, /= temperature, softmax, coin, sample_top_p).
  * The whole step runs on the device; `coin` is the host's random_f32 draw.  top6 (optional): the six most probable ids (observation hook). */
-int nb200_next_sampled(nb200_engine *e, const uint32_t *ids, uint32_t pos, float penalty, float temperature, float top_p, float coin,
+static int nano_next_sampled(nb200_engine *e, const uint32_t *ids, uint32_t pos, float penalty, float temperature, float top_p, float coin,
                        uint32_t *next, uint32_t *top6) {
     if (!e || !ids || !next) return fail(NB200_EINVAL, "null argument");
     if (pos >= e->d.max_seq || ids[pos] >= e->d.V) return fail(NB200_EINVAL, "token/pos out of range");
@@ -1235,7 +1222,7 @@ int nb200_next_sampled(nb200_engine *e, const uint32_t *ids, uint32_t pos, float
     return 0;
 }
 
-int nb200_decode_greedy(nb200_engine *e, uint32_t *ids, uint32_t n_prompt, uint32_t n_total, float penalty,
+static int nano_decode_greedy(nb200_engine *e, uint32_t *ids, uint32_t n_prompt, uint32_t n_total, float penalty,
                         float *prefill_ms, float *device_ms) {
     if (!e || !ids) return fail(NB200_EINVAL, "null argument");
     if (n_prompt < 1 || n_total < n_prompt || n_total > e->d.max_seq + 1) return fail(NB200_EINVAL, "bad n_prompt/n_total");
@@ -1267,6 +1254,7 @@ int nb200_decode_greedy(nb200_engine *e, uint32_t *ids, uint32_t n_prompt, uint3
 }
 
 int nb200_read_buffer(nb200_engine *e, int field, uint32_t layer, uint32_t pos, float *dst, uint32_t count) {
+    NANO_ONLY(e);
     if (!e || !dst) return fail(NB200_EINVAL, "null argument");
     CK(cudaSetDevice(e->device));
     CK(cudaStreamSynchronize(e->stream));
@@ -1300,6 +1288,7 @@ int nb200_read_buffer(nb200_engine *e, int field, uint32_t layer, uint32_t pos, 
 }
 
 int nb200_write_x(nb200_engine *e, const float *x, uint32_t count) {
+    NANO_ONLY(e);
     if (!e || !x || count != e->d.E) return fail(NB200_EINVAL, "bad argument");
     if (e->tp_size > 1) return fail(NB200_EINVAL, "not available on tensor-parallel engines");
     CK(cudaSetDevice(e->device));
@@ -1309,6 +1298,7 @@ int nb200_write_x(nb200_engine *e, const float *x, uint32_t count) {
 }
 
 int nb200_run_layer(nb200_engine *e, uint32_t layer, uint32_t pos, uint32_t is_causal) {
+    NANO_ONLY(e);
     if (!e || layer >= e->d.L || pos >= e->d.max_seq) return fail(NB200_EINVAL, "bad argument");
     if (e->tp_size > 1) return fail(NB200_EINVAL, "not available on tensor-parallel engines");
     CK(cudaSetDevice(e->device));
@@ -1323,6 +1313,7 @@ int nb200_run_layer(nb200_engine *e, uint32_t layer, uint32_t pos, uint32_t is_c
 // around every kernel; accumulates device milliseconds and launch counts per kernel class:
 // 0 embed, 1 qkv, 2 attention, 3 o-proj, 4 w1|w3, 5 w2, 6 classifier.
 int nb200_profile_tokens(nb200_engine *e, const uint32_t *ids, uint32_t start, uint32_t n, float ms[7], uint32_t counts[7]) {
+    NANO_ONLY(e);
     if (!e || !ids || !ms || !counts) return fail(NB200_EINVAL, "null argument");
     if (start + n > e->d.max_seq) return fail(NB200_EINVAL, "range exceeds max_seq_len");
     CK(cudaSetDevice(e->device));
@@ -1347,6 +1338,7 @@ int nb200_profile_tokens(nb200_engine *e, const uint32_t *ids, uint32_t start, u
 
 // Debug (NB200_ATTN_DBG=1 at engine creation): the 32 %globaltimer stamps (ns) of the last run of layer L/2's attention kernel.
 int nb200_read_attn_trace(nb200_engine *e, unsigned long long *stamps32) {
+    NANO_ONLY(e);
     if (!e || !stamps32 || !e->attn_dbg) return fail(NB200_EINVAL, "attention trace not enabled (NB200_ATTN_DBG=1)");
     CK(cudaSetDevice(e->device));
     CK(cudaStreamSynchronize(e->stream));
@@ -1356,6 +1348,7 @@ int nb200_read_attn_trace(nb200_engine *e, unsigned long long *stamps32) {
 
 // Debug: per-barrier clock64() stamps of CTA 0 for one token through the persistent kernel (5L+3 stamps + 1).
 int nb200_trace_token(nb200_engine *e, uint32_t token, uint32_t pos, unsigned long long *stamps, uint32_t cap, uint32_t *count) {
+    NANO_ONLY(e);
     if (!e || !stamps || !count) return fail(NB200_EINVAL, "null argument");
     if (!e->use_stream) return fail(NB200_EINVAL, "persistent kernel not active");
     CK(cudaSetDevice(e->device));
@@ -1374,9 +1367,8 @@ int nb200_trace_token(nb200_engine *e, uint32_t token, uint32_t pos, unsigned lo
     return r;
 }
 
-uint64_t nb200_kernel_launches(const nb200_engine *e) { return e ? e->launches : 0; }
-uint32_t nb200_launches_per_token(const nb200_engine *e) { return e ? e->launches_per_token : 0; }
-uint64_t nb200_weight_bytes(const nb200_engine *e) { return e ? e->weight_bytes : 0; }
+const nb::EngineOps kNanoOps = {nano_destroy, nano_get_config, nano_forward, nano_read_logits, nano_next_greedy, nano_next_sampled,
+                               nano_decode_greedy, nullptr, nullptr, nullptr, nullptr, nullptr};
 
 // ---------------------------------------------------------------------------------------------
 // op-level entry points

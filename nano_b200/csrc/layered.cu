@@ -1,0 +1,823 @@
+// layered.cu -- the layered model family of libnano_b200.so: decoders described by config.json as a list of typed layers
+// (a token mixer + an optional feed-forward each, over an fp32 residual stream), loaded from model.safetensors.
+//
+// Registered design: "Famudra" -- parallel layers  x <- x + (mixer(shift(norm1 x)) + ff(norm2 x))  with scalar-gain RMS norms and a
+// token shift on the mixer input; mixers "rglru" (gelu branch x conv + real-gated linear recurrent unit) and "latent_attention"
+// (queries and keys/values through normed low-rank latents, no positions, causal softmax); feed-forward "moe" (top-k routed
+// squared-relu experts + a shared expert); a span of layers may run several times with the same weights ("loop"), each pass with
+// cache and state of its own and the embedding output added again before every pass but the first.
+//
+// Host side of the family:
+//   loader         config -> layer table; tensors -> HBM in the compute type (bf16 as stored, or widened to fp32 with NB200_FLAG_F32),
+//                  fused where one product serves two projections ([y | x] of the recurrent block, [query latent | kv latent],
+//                  [recurrence gate | input gate] blocks, experts stacked), W_uk transposed per head so queries can be absorbed
+//   state manager  sequences = {cache pages, one state slot}.  Pages of kPage tokens come from a LIFO free list and hold the latent
+//                  rows of EVERY attention layer run; a slot holds, per layer run, the previous mixer input (token shift) and, for a
+//                  recurrent run, the fp32 state and the convolution tail.  Slots are zeroed when a sequence opens.
+//   step           a portion of n tokens is cut into chunks of <= chunk_cap tokens; each chunk runs every layer run with the prefill
+//                  kernels (n > kGemvMaxM) or the decode kernels; logits only where asked
+//   generation     the C-ABI's forward / next_greedy / next_sampled / decode_greedy on one implicit sequence; the greedy loop feeds
+//                  the chosen token back on the device
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "family.h"
+#include "layered_kernels.cuh"
+#include "modeldir.h"
+#include "sample_host.h"
+
+using nb::fail;
+using namespace nb::lm;
+
+#define CK(call) NB_CK(call)
+
+namespace {
+
+struct Weight { void *p = nullptr; uint32_t rows = 0, cols = 0; };
+
+enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1 };
+
+struct Layer {
+    int type = 0;
+    float *norm1 = nullptr, *norm2 = nullptr, *shift = nullptr;
+    // rglru
+    uint32_t C = 0, blocks = 0, taps = 0;
+    Weight yx, gates, o;
+    float *yx_b = nullptr, *conv = nullptr, *conv_b = nullptr, *gates_b = nullptr, *lam = nullptr;
+    // latent attention
+    uint32_t H = 0, dim = 0, vdim = 0, R = 0, QR = 0; float scale = 0.0f;
+    Weight dqkv, uq, ukT, uv;
+    float *dq_norm = nullptr, *dkv_norm = nullptr;
+    // feed-forward
+    bool has_mlp = false, has_shared = false;
+    uint32_t NE = 0, top = 0, ff = 0, sff = 0;
+    float *router = nullptr;
+    Weight up, down, sup, sdown;
+};
+
+struct Run { uint32_t layer = 0; bool add_embed = false; size_t st_prev = 0, st_S = 0, st_conv = 0; float *cache = nullptr; };
+
+struct Seq { bool live = false; uint32_t len = 0; std::vector<uint32_t> pages; };
+
+constexpr float kRglruDecay = 8.0f;      // a = exp(-8 r softplus(lam)): fixed by the design
+constexpr uint32_t kWantBatch = 64;      // rows of logits computed per head product
+constexpr uint32_t kSplitMax = 32;
+
+}  // namespace
+
+struct LayeredEngine : nb::EngineBase {
+    int device = 0, num_sms = 148;
+    cudaStream_t stream = nullptr;
+    bool f32 = false;
+    uint32_t V = 0, E = 0; float eps = 0.0f;
+    std::vector<Layer> layers; std::vector<Run> runs;
+    bool keep_x0 = false;
+    Weight embed, head; float *final_norm = nullptr;
+    // state manager
+    uint32_t max_tokens = 0, max_seqs = 0, n_pages = 0, chunk_cap = 0; size_t slot_floats = 0;
+    float *state = nullptr, *state_bak = nullptr; uint32_t *table = nullptr;
+    std::vector<uint32_t> free_pages; std::vector<Seq> seqs;
+    // scratch (chunk_cap tokens)
+    float *x = nullptr, *x0 = nullptr, *hm = nullptr, *h2 = nullptr, *d = nullptr;
+    float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
+    float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
+    float *b_zr = nullptr, *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
+    uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
+    float *b_xn = nullptr, *logits = nullptr, *keep = nullptr;
+    uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
+    uint32_t last_T = 0;
+    // generation on the implicit sequence
+    int gen_seq = -1;
+    void *samp_ws = nullptr; size_t samp_cub = 0; uint32_t *samp_host = nullptr;
+    std::vector<void *> allocs;
+};
+
+namespace {
+
+inline LayeredEngine *self(nb200_engine *e) { return reinterpret_cast<LayeredEngine *>(e); }
+inline const LayeredEngine *self(const nb200_engine *e) { return reinterpret_cast<const LayeredEngine *>(e); }
+
+int dmalloc(LayeredEngine *e, void **p, size_t bytes) {
+    if (bytes == 0) bytes = 16;
+    cudaError_t err = cudaMalloc(p, bytes);
+    if (err != cudaSuccess) return fail(NB200_ENOMEM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(err));
+    e->allocs.push_back(*p);
+    return 0;
+}
+#define DM(ptr, bytes) do { int r_ = dmalloc(e, (void **)&(ptr), (bytes)); if (r_) return r_; } while (0)
+
+// ---------------- loader ----------------
+struct Loader {
+    LayeredEngine *e; const nb::ModelDir *dir;
+
+    int host_f32(const std::string &name, std::vector<float> *out, std::vector<uint64_t> *shape) {
+        auto it = dir->tensors.find(name);
+        if (it == dir->tensors.end()) return fail(NB200_EINVAL, "model.safetensors has no tensor \"%s\"", name.c_str());
+        const nb::StTensor &t = it->second;
+        const uint64_t n = t.count();
+        out->resize(n);
+        if (t.dtype == "BF16") {
+            const uint16_t *s = reinterpret_cast<const uint16_t *>(t.data);
+            for (uint64_t i = 0; i < n; i++) { const uint32_t u = (uint32_t)s[i] << 16; memcpy(&(*out)[i], &u, 4); }
+        } else if (t.dtype == "F32") {
+            memcpy(out->data(), t.data, n * 4);
+        } else return fail(NB200_EINVAL, "tensor \"%s\" has dtype %s (BF16 or F32 expected)", name.c_str(), t.dtype.c_str());
+        if (shape) *shape = t.shape;
+        return 0;
+    }
+    int expect(const std::string &name, const std::vector<uint64_t> &got, std::initializer_list<uint64_t> want) {
+        if (got.size() != want.size() || !std::equal(got.begin(), got.end(), want.begin())) {
+            std::string g, w;
+            for (uint64_t v : got) g += std::to_string(v) + " ";
+            for (uint64_t v : want) w += std::to_string(v) + " ";
+            return fail(NB200_EINVAL, "tensor \"%s\" has shape [ %s] where the config implies [ %s]", name.c_str(), g.c_str(), w.c_str());
+        }
+        return 0;
+    }
+    // fp32 vector (norm gains, biases, taps, router): stays fp32 in every mode
+    int vec(const std::string &name, std::initializer_list<uint64_t> shape, float **dst) {
+        std::vector<float> h; std::vector<uint64_t> sh; int r;
+        if ((r = host_f32(name, &h, &sh)) || (r = expect(name, sh, shape))) return r;
+        return put_f32(h, dst);
+    }
+    int put_f32(const std::vector<float> &h, float **dst) {
+        DM(*dst, h.size() * 4);
+        CK(cudaMemcpy(*dst, h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+        e->weight_bytes += h.size() * 4;
+        return 0;
+    }
+    // matrix in the compute type
+    int put_w(const std::vector<float> &h, uint32_t rows, uint32_t cols, Weight *w) {
+        w->rows = rows; w->cols = cols;
+        if (e->f32) { float *p = nullptr; int r = put_f32(h, &p); w->p = p; return r; }
+        std::vector<__nv_bfloat16> b(h.size());
+        for (size_t i = 0; i < h.size(); i++) b[i] = __float2bfloat16_rn(h[i]);
+        DM(w->p, b.size() * 2);
+        CK(cudaMemcpy(w->p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
+        e->weight_bytes += b.size() * 2;
+        return 0;
+    }
+    // rows of several [r_i, cols] tensors stacked into one matrix
+    int stacked(const std::vector<std::string> &names, const std::vector<uint64_t> &rows, uint64_t cols, Weight *w) {
+        std::vector<float> all;
+        uint64_t total = 0;
+        for (size_t i = 0; i < names.size(); i++) {
+            std::vector<float> h; std::vector<uint64_t> sh; int r;
+            if ((r = host_f32(names[i], &h, &sh)) || (r = expect(names[i], sh, {rows[i], cols}))) return r;
+            all.insert(all.end(), h.begin(), h.end());
+            total += rows[i];
+        }
+        return put_w(all, (uint32_t)total, (uint32_t)cols, w);
+    }
+};
+
+bool u32_of(const nb::Json *o, const char *key, uint32_t *v) {
+    double d;
+    if (!o || !o->number(key, &d) || d < 0 || d > 4294967295.0 || d != (double)(uint64_t)d) return false;
+    *v = (uint32_t)d;
+    return true;
+}
+
+int load_rglru(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(m, "width", &L->C) || !u32_of(m, "blocks", &L->blocks) || !u32_of(m, "conv", &L->taps))
+        return fail(NB200_EINVAL, "%s: an rglru mixer needs width, blocks and conv", p.c_str());
+    if (!L->C || !L->blocks || !L->taps || L->C % L->blocks) return fail(NB200_EINVAL, "%s: width %u / blocks %u / conv %u unusable", p.c_str(), L->C, L->blocks, L->taps);
+    const uint64_t C = L->C, B = L->blocks, bs = C / B;
+    int r;
+    if ((r = ld.stacked({p + "y", p + "x"}, {C, C}, E, &L->yx))) return r;
+    {
+        std::vector<float> a, b; std::vector<uint64_t> sa, sb;
+        if ((r = ld.host_f32(p + "y.b", &a, &sa)) || (r = ld.expect(p + "y.b", sa, {C})) || (r = ld.host_f32(p + "x.b", &b, &sb)) || (r = ld.expect(p + "x.b", sb, {C}))) return r;
+        a.insert(a.end(), b.begin(), b.end());
+        if ((r = ld.put_f32(a, &L->yx_b))) return r;
+    }
+    if ((r = ld.vec(p + "conv", {C, L->taps}, &L->conv)) || (r = ld.vec(p + "conv.b", {C}, &L->conv_b)) || (r = ld.vec(p + "lam", {C}, &L->lam))) return r;
+    {   // [recurrence gate blocks | input gate blocks], each block [bs, bs]
+        std::vector<float> a, b, ab, bb; std::vector<uint64_t> s;
+        if ((r = ld.host_f32(p + "ra", &a, &s)) || (r = ld.expect(p + "ra", s, {B, bs, bs})) || (r = ld.host_f32(p + "ri", &b, &s)) || (r = ld.expect(p + "ri", s, {B, bs, bs})) ||
+            (r = ld.host_f32(p + "ra.b", &ab, &s)) || (r = ld.expect(p + "ra.b", s, {B, bs})) || (r = ld.host_f32(p + "ri.b", &bb, &s)) || (r = ld.expect(p + "ri.b", s, {B, bs}))) return r;
+        a.insert(a.end(), b.begin(), b.end());
+        ab.insert(ab.end(), bb.begin(), bb.end());
+        if ((r = ld.put_w(a, (uint32_t)(2 * C), (uint32_t)bs, &L->gates)) || (r = ld.put_f32(ab, &L->gates_b))) return r;
+    }
+    return ld.stacked({p + "o"}, {E}, C, &L->o);
+}
+
+int load_latent_attn(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E) {
+    double sc;
+    if (!u32_of(m, "heads", &L->H) || !u32_of(m, "dim", &L->dim) || !u32_of(m, "vdim", &L->vdim) || !u32_of(m, "kv_rank", &L->R) || !u32_of(m, "q_rank", &L->QR) ||
+        !m->number("scale", &sc))
+        return fail(NB200_EINVAL, "%s: a latent_attention mixer needs heads, dim, vdim, kv_rank, q_rank and scale", p.c_str());
+    L->scale = (float)sc;
+    if (!L->H || !L->dim || !L->vdim || !L->R || !L->QR) return fail(NB200_EINVAL, "%s: zero-sized attention", p.c_str());
+    if (L->R > 512) return fail(NB200_EINVAL, "%s: kv_rank %u above 512 has no attention kernel", p.c_str(), L->R);
+    const uint64_t H = L->H, D = L->dim, VD = L->vdim, R = L->R, QR = L->QR;
+    int r;
+    if ((r = ld.stacked({p + "dq", p + "dkv"}, {QR, R}, E, &L->dqkv)) || (r = ld.vec(p + "dq.norm", {QR}, &L->dq_norm)) || (r = ld.vec(p + "dkv.norm", {R}, &L->dkv_norm)) ||
+        (r = ld.stacked({p + "uq"}, {H * D}, QR, &L->uq)) || (r = ld.stacked({p + "uv"}, {H * VD}, R, &L->uv)) || (r = ld.stacked({p + "o"}, {E}, H * VD, &L->o))) return r;
+    std::vector<float> uk, t(H * R * D); std::vector<uint64_t> s;
+    if ((r = ld.host_f32(p + "uk", &uk, &s)) || (r = ld.expect(p + "uk", s, {H * D, R}))) return r;
+    for (uint64_t h = 0; h < H; h++)          // [H*dim, R] -> per head [R, dim]: absorbed query = q_h W_uk,h
+        for (uint64_t dd = 0; dd < D; dd++)
+            for (uint64_t k = 0; k < R; k++) t[(h * R + k) * D + dd] = uk[(h * D + dd) * R + k];
+    return ld.put_w(t, (uint32_t)(H * R), (uint32_t)D, &L->ukT);
+}
+
+int load_moe(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+    const nb::Json *kind = f->get("kind");
+    if (!kind || kind->t != nb::Json::Str || kind->str != "moe") return fail(NB200_EINVAL, "%s: feed-forward kind \"%s\" is not known", p.c_str(), kind && kind->t == nb::Json::Str ? kind->str.c_str() : "?");
+    if (!u32_of(f->get("router"), "experts", &L->NE) || !u32_of(f->get("router"), "top", &L->top) || !u32_of(f->get("expert"), "ff", &L->ff))
+        return fail(NB200_EINVAL, "%s: a moe feed-forward needs router.experts, router.top and expert.ff", p.c_str());
+    if (!L->NE || !L->top || L->top > L->NE || !L->ff) return fail(NB200_EINVAL, "%s: experts %u / top %u / ff %u unusable", p.c_str(), L->NE, L->top, L->ff);
+    L->has_mlp = true;
+    int r;
+    if ((r = ld.vec(p + "router", {L->NE, E}, &L->router))) return r;
+    std::vector<std::string> ups, downs; std::vector<uint64_t> ur, dr;
+    for (uint32_t i = 0; i < L->NE; i++) { ups.push_back(p + "e" + std::to_string(i) + ".up"); downs.push_back(p + "e" + std::to_string(i) + ".down"); ur.push_back(L->ff); dr.push_back(E); }
+    if ((r = ld.stacked(ups, ur, E, &L->up)) || (r = ld.stacked(downs, dr, L->ff, &L->down))) return r;
+    if (f->present("shared")) {
+        if (!u32_of(f->get("shared"), "ff", &L->sff) || !L->sff) return fail(NB200_EINVAL, "%s: shared.ff missing", p.c_str());
+        L->has_shared = true;
+        if ((r = ld.stacked({p + "shared.up"}, {L->sff}, E, &L->sup)) || (r = ld.stacked({p + "shared.down"}, {E}, L->sff, &L->sdown))) return r;
+    }
+    return 0;
+}
+
+// ---------------- launches ----------------
+template <typename A>
+int launch(LayeredEngine *e, void (*k)(const A), dim3 grid, dim3 block, size_t smem, const A &args) {
+    k<<<grid, block, smem, e->stream>>>(args);
+    CK(cudaGetLastError());
+    e->launches++;
+    return 0;
+}
+
+// one matrix product; maxM = the most rows any group can have.  wf32: the weights are fp32 whatever the engine's mode (router)
+int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32 = false) {
+    if (!a.a_gmod) a.a_gmod = 1;
+    const bool f32 = e->f32 || wf32;
+    if (maxM <= kGemvMaxM) {
+        a.round_a = f32 ? 0u : 1u;
+        uint32_t gx = (a.N + 7u) / 8u;
+        const uint32_t cap = std::max(1u, (uint32_t)e->num_sms * 8u / groups);
+        gx = std::min(gx, cap);
+        return f32 ? launch<GemmArgs>(e, k_gemv<float>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv<__nv_bfloat16>, dim3(gx, groups), dim3(256), 0, a);
+    }
+    const dim3 grid((a.N + 63u) / 64u, (maxM + 63u) / 64u, groups);
+    return f32 ? launch<GemmArgs>(e, k_gemm_f32<float>, grid, dim3(256), 0, a) : launch<GemmArgs>(e, k_gemm_bf16, grid, dim3(128), 0, a);
+}
+
+GemmArgs plain(const float *A, uint32_t lda, const Weight &w, float *C, uint32_t ldc, uint32_t M, const float *bias = nullptr, uint32_t epi = EPI_NONE, uint32_t split = 0) {
+    GemmArgs a{};
+    a.A = A; a.lda = lda; a.W = w.p; a.ldw = w.cols; a.C = C; a.ldc = ldc; a.M = M; a.N = w.rows; a.K = w.cols; a.bias = bias;
+    a.epi = bias && epi == EPI_NONE ? EPI_BIAS : epi; a.split = split; a.a_gmod = 1;
+    return a;
+}
+
+uint32_t ew_grid(size_t n) { return (uint32_t)std::min<size_t>((n + 255) / 256, 148 * 16); }
+
+int attn_launch(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
+    const size_t smem = ((size_t)kAttnWarps * a.R + (size_t)kPage * (a.R + 1)) * 4;
+    const dim3 grid(a.T, a.nsplit, (a.H + kAttnWarps - 1) / kAttnWarps), block(kAttnWarps * 32);
+    if (rch <= 2) return launch<AttnArgs>(e, k_latent_attn<2>, grid, block, smem, a);
+    if (rch <= 4) return launch<AttnArgs>(e, k_latent_attn<4>, grid, block, smem, a);
+    if (rch <= 8) return launch<AttnArgs>(e, k_latent_attn<8>, grid, block, smem, a);
+    return launch<AttnArgs>(e, k_latent_attn<16>, grid, block, smem, a);
+}
+
+// every layer run over T tokens (x already holds their embeddings) of the sequence in `slot`, whose first token sits at pos0
+int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0) {
+    const uint32_t E = e->E;
+    float *st = e->state + (size_t)slot * e->slot_floats;
+    const uint32_t *table = e->table + (size_t)slot * e->n_pages;
+    int r;
+    for (size_t ri = 0; ri < e->runs.size(); ri++) {
+        const Run &run = e->runs[ri];
+        const Layer &L = e->layers[run.layer];
+        if (run.add_embed) { k_add<<<ew_grid((size_t)T * E), 256, 0, e->stream>>>(e->x, e->x0, (size_t)T * E); CK(cudaGetLastError()); e->launches++; }
+        {
+            NormShiftArgs a{e->x, L.norm1, L.has_mlp ? L.norm2 : nullptr, L.shift, st + run.st_prev, e->hm, L.has_mlp ? e->h2 : nullptr, T, E, e->eps};
+            if ((r = launch<NormShiftArgs>(e, k_norm_shift, dim3(T > 1 ? T - 1 : 1), dim3(256), 0, a))) return r;
+        }
+        if (L.type == MIX_RGLRU) {
+            const uint32_t C = L.C, bs = C / L.blocks;
+            if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
+            ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
+            if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
+            if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
+            GemmArgs g{};
+            g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
+            g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
+            if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
+            ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
+            if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r;
+            if ((r = gemm(e, plain(e->b_sy, C, L.o, e->d, E, T), 1, T))) return r;
+        } else {
+            const uint32_t H = L.H, R = L.R, QR = L.QR;
+            if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
+            LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps};
+            if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
+            if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+            GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
+            g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
+            g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
+            if ((r = gemm(e, g, H, T))) return r;
+            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale};
+            if (T <= kGemvMaxM) {
+                const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
+                aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 4u));
+            }
+            if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
+            if (aa.nsplit > 1 && (r = launch<AttnArgs>(e, k_attn_merge, dim3(T, H), dim3(64), 0, aa))) return r;
+            GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
+            v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
+            v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
+            if ((r = gemm(e, v, H, T))) return r;
+            if ((r = gemm(e, plain(e->b_ov, H * L.vdim, L.o, e->d, E, T), 1, T))) return r;
+        }
+        CombineArgs c{e->x, e->d, nullptr, nullptr, nullptr, nullptr, e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr, T, E, 0};
+        if (L.has_mlp) {
+            Weight rw; rw.p = L.router; rw.rows = L.NE; rw.cols = E;
+            if ((r = gemm(e, plain(e->h2, E, rw, e->b_zr, L.NE, T), 1, T, true))) return r;
+            RouteArgs ra{e->b_zr, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top};
+            if ((r = launch<RouteArgs>(e, k_route, dim3((T + 63) / 64), dim3(64), 0, ra)) || (r = launch<RouteArgs>(e, k_route_scan, dim3(1), dim3(32), 0, ra)) ||
+                (r = launch<RouteArgs>(e, k_route_scatter, dim3((T * L.top + 127) / 128), dim3(128), 0, ra))) return r;
+            GemmArgs u{};
+            u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.C = e->b_hb; u.ldc = L.ff; u.M = T; u.N = L.ff; u.K = E; u.a_gmod = 1;
+            u.g_off = e->b_off; u.a_rows = e->b_rows; u.w_gstride = (uint64_t)L.ff * E; u.epi = EPI_RELU2;
+            if ((r = gemm(e, u, L.NE, T))) return r;
+            GemmArgs dn{};
+            dn.A = e->b_hb; dn.lda = L.ff; dn.W = L.down.p; dn.ldw = L.ff; dn.C = e->b_eo; dn.ldc = E; dn.M = T; dn.N = E; dn.K = L.ff; dn.a_gmod = 1;
+            dn.g_off = e->b_off; dn.w_gstride = (uint64_t)E * L.ff;
+            if ((r = gemm(e, dn, L.NE, T))) return r;
+            if (L.has_shared) {
+                if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, L.sff, T, nullptr, EPI_RELU2), 1, T)) || (r = gemm(e, plain(e->b_sh, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
+            }
+            c.eo = e->b_eo; c.slot = e->b_slot; c.wt = e->b_wt; c.shared = L.has_shared ? e->b_so : nullptr; c.top = L.top;
+        }
+        if ((r = launch<CombineArgs>(e, k_combine, dim3(ew_grid((size_t)T * E)), dim3(256), 0, c))) return r;
+    }
+    e->last_T = T;
+    return 0;
+}
+
+int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T) {
+    if (e->f32) k_embed<float><<<T, 128, 0, e->stream>>>(tok_dev, (const float *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
+    else k_embed<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, (const __nv_bfloat16 *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
+    CK(cudaGetLastError());
+    e->launches++;
+    return 0;
+}
+
+// logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
+int head_rows(LayeredEngine *e, uint32_t nw) {
+    k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);
+}
+
+// ---------------- state manager ----------------
+int seq_check(LayeredEngine *e, uint32_t seq) {
+    if (seq >= e->seqs.size() || !e->seqs[seq].live) return fail(NB200_EINVAL, "sequence %u is not open", seq);
+    return 0;
+}
+
+int reserve_pages(LayeredEngine *e, uint32_t seq, uint32_t tokens) {
+    Seq &s = e->seqs[seq];
+    const size_t have = s.pages.size(), need = (tokens + kPage - 1) / kPage;
+    if (need <= have) return 0;
+    if (need - have > e->free_pages.size()) return fail(NB200_ENOMEM, "the cache is full: %u tokens asked for sequence %u, %zu pages free", tokens, seq, e->free_pages.size());
+    for (size_t i = have; i < need; i++) { s.pages.push_back(e->free_pages.back()); e->free_pages.pop_back(); }
+    CK(cudaMemcpyAsync(e->table + (size_t)seq * e->n_pages + have, s.pages.data() + have, (need - have) * 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaStreamSynchronize(e->stream));      // the source is pageable host memory owned by the vector
+    return 0;
+}
+
+int lm_seq_open(nb200_engine *h, uint32_t *seq) {
+    LayeredEngine *e = self(h);
+    if (!seq) return fail(NB200_EINVAL, "null argument");
+    CK(cudaSetDevice(e->device));
+    for (uint32_t i = 0; i < e->seqs.size(); i++) {
+        if (e->seqs[i].live) continue;
+        e->seqs[i].live = true; e->seqs[i].len = 0; e->seqs[i].pages.clear();
+        CK(cudaMemsetAsync(e->state + (size_t)i * e->slot_floats, 0, e->slot_floats * 4, e->stream));
+        *seq = i;
+        return 0;
+    }
+    return fail(NB200_ENOMEM, "all %u sequence slots are in use", e->max_seqs);
+}
+
+int lm_seq_close(nb200_engine *h, uint32_t seq) {
+    LayeredEngine *e = self(h);
+    int r;
+    if ((r = seq_check(e, seq))) return r;
+    Seq &s = e->seqs[seq];
+    for (size_t i = s.pages.size(); i > 0; i--) e->free_pages.push_back(s.pages[i - 1]);
+    s.pages.clear(); s.live = false; s.len = 0;
+    if ((int)seq == e->gen_seq) e->gen_seq = -1;
+    return 0;
+}
+
+// ---------------- step ----------------
+// tokens already on the device at tok_dev[0..n); want (host, ascending, may be null) -> logits_host [n_want][V]
+int step_dev(LayeredEngine *e, uint32_t seq, const uint32_t *tok_dev, uint32_t n, const uint32_t *want, uint32_t n_want, float *logits_host) {
+    int r;
+    Seq &s = e->seqs[seq];
+    if ((r = reserve_pages(e, seq, s.len + n))) return r;
+    uint32_t wi = 0;
+    for (uint32_t c0 = 0; c0 < n; c0 += e->chunk_cap) {
+        const uint32_t T = std::min(e->chunk_cap, n - c0);
+        if ((r = embed_tokens(e, tok_dev + c0, T)) || (r = run_layers(e, seq, T, s.len))) return r;
+        s.len += T;
+        while (wi < n_want && want[wi] < c0 + T) {
+            uint32_t idx[kWantBatch], nw = 0;
+            while (nw < kWantBatch && wi + nw < n_want && want[wi + nw] < c0 + T) { idx[nw] = want[wi + nw] - c0; nw++; }
+            CK(cudaMemcpyAsync(e->want_dev, idx, nw * 4, cudaMemcpyHostToDevice, e->stream));
+            CK(cudaStreamSynchronize(e->stream));
+            if ((r = head_rows(e, nw))) return r;
+            CK(cudaMemcpyAsync(logits_host + (size_t)wi * e->V, e->logits, (size_t)nw * e->V * 4, cudaMemcpyDeviceToHost, e->stream));
+            CK(cudaStreamSynchronize(e->stream));
+            wi += nw;
+        }
+    }
+    return 0;
+}
+
+int check_tokens(LayeredEngine *e, const uint32_t *tokens, uint32_t n) {
+    for (uint32_t i = 0; i < n; i++) if (tokens[i] >= e->V) return fail(NB200_EINVAL, "token id %u outside the vocabulary of %u", tokens[i], e->V);
+    return 0;
+}
+
+int lm_step(nb200_engine *h, uint32_t seq, const uint32_t *tokens, uint32_t n, const uint32_t *want, uint32_t n_want, float *logits) {
+    LayeredEngine *e = self(h);
+    int r;
+    if (!tokens || n == 0 || (n_want && (!want || !logits))) return fail(NB200_EINVAL, "bad arguments");
+    if ((r = seq_check(e, seq)) || (r = check_tokens(e, tokens, n))) return r;
+    for (uint32_t i = 0; i < n_want; i++) if (want[i] >= n || (i && want[i] <= want[i - 1])) return fail(NB200_EINVAL, "want[] must be ascending indices into this step's tokens");
+    CK(cudaSetDevice(e->device));
+    std::vector<uint32_t> done;
+    for (uint32_t c0 = 0; c0 < n; c0 += e->max_tokens) {          // the staging buffer holds max_tokens ids
+        const uint32_t m = std::min(e->max_tokens, n - c0);
+        CK(cudaMemcpyAsync(e->ids_dev, tokens + c0, (size_t)m * 4, cudaMemcpyHostToDevice, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        uint32_t w0 = 0, w1 = 0;
+        while (w0 < n_want && want[w0] < c0) w0++;
+        w1 = w0;
+        done.clear();
+        while (w1 < n_want && want[w1] < c0 + m) done.push_back(want[w1++] - c0);
+        if ((r = step_dev(e, seq, e->ids_dev, m, done.data(), (uint32_t)done.size(), logits ? logits + (size_t)w0 * e->V : nullptr))) return r;
+    }
+    CK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int lm_step_timed(nb200_engine *h, uint32_t seq, const uint32_t *tokens, uint32_t n, uint32_t reps, float *ms) {
+    LayeredEngine *e = self(h);
+    int r;
+    if (!tokens || !n || !reps || !ms || n > e->max_tokens) return fail(NB200_EINVAL, "bad arguments");
+    if ((r = seq_check(e, seq)) || (r = check_tokens(e, tokens, n))) return r;
+    CK(cudaSetDevice(e->device));
+    float *slot = e->state + (size_t)seq * e->slot_floats;
+    const uint32_t len0 = e->seqs[seq].len;
+    CK(cudaMemcpyAsync(e->ids_dev, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemcpyAsync(e->state_bak, slot, e->slot_floats * 4, cudaMemcpyDeviceToDevice, e->stream));
+    cudaEvent_t ev[2];
+    CK(cudaEventCreate(&ev[0])); CK(cudaEventCreate(&ev[1]));
+    float total = 0.0f;
+    for (uint32_t rep = 0; rep <= reps; rep++) {           // rep 0 is the untimed run
+        CK(cudaMemcpyAsync(slot, e->state_bak, e->slot_floats * 4, cudaMemcpyDeviceToDevice, e->stream));
+        e->seqs[seq].len = len0;
+        CK(cudaEventRecord(ev[0], e->stream));
+        if ((r = step_dev(e, seq, e->ids_dev, n, nullptr, 0, nullptr))) break;
+        CK(cudaEventRecord(ev[1], e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        float t = 0.0f;
+        CK(cudaEventElapsedTime(&t, ev[0], ev[1]));
+        if (rep) total += t;
+    }
+    cudaEventDestroy(ev[0]); cudaEventDestroy(ev[1]);
+    if (r) return r;
+    *ms = total / (float)reps;
+    return 0;
+}
+
+int lm_read_residual(nb200_engine *h, uint32_t run, float *dst, uint32_t count) {
+    LayeredEngine *e = self(h);
+    if (!e->keep) return fail(NB200_EINVAL, "residuals are kept only by engines created with NB200_KEEP_RESIDUALS=1");
+    if (run >= e->runs.size() || !dst || count > e->last_T * e->E) return fail(NB200_EINVAL, "bad run / count");
+    CK(cudaSetDevice(e->device));
+    CK(cudaMemcpyAsync(dst, e->keep + (size_t)run * e->chunk_cap * e->E, (size_t)count * 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+// ---------------- generation on the implicit sequence ----------------
+int gen_reset(LayeredEngine *e) {
+    int r;
+    if (e->gen_seq >= 0 && (r = lm_seq_close(reinterpret_cast<nb200_engine *>(e), (uint32_t)e->gen_seq))) return r;
+    uint32_t s = 0;
+    if ((r = lm_seq_open(reinterpret_cast<nb200_engine *>(e), &s))) return r;
+    e->gen_seq = (int)s;
+    return 0;
+}
+
+// brings the implicit sequence to `pos` tokens: pos 0 starts over; tokens between its length and pos come from ids[]
+int gen_seek(LayeredEngine *e, const uint32_t *ids, uint32_t pos) {
+    int r;
+    if (pos == 0 || e->gen_seq < 0) { if ((r = gen_reset(e))) return r; }
+    Seq &s = e->seqs[e->gen_seq];
+    if (pos < s.len) return fail(NB200_EINVAL, "position %u lies before the %u tokens this engine has consumed (positions arrive in order; 0 starts over)", pos, s.len);
+    if (pos > s.len) {
+        if (!ids) return fail(NB200_EINVAL, "position %u skips tokens %u..%u", pos, s.len, pos - 1);
+        const uint32_t n = pos - s.len;
+        if ((r = check_tokens(e, ids + s.len, n))) return r;
+        if (n > e->max_tokens) return fail(NB200_EINVAL, "portion longer than the engine's max_tokens");
+        CK(cudaMemcpyAsync(e->ids_dev, ids + s.len, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        if ((r = step_dev(e, (uint32_t)e->gen_seq, e->ids_dev, n, nullptr, 0, nullptr))) return r;
+    }
+    return 0;
+}
+
+// one token of the implicit sequence; its logits end in e->logits[0..V)
+int gen_token(LayeredEngine *e, uint32_t token) {
+    int r;
+    if (token >= e->V) return fail(NB200_EINVAL, "token/pos out of range");
+    const uint32_t zero = 0;
+    CK(cudaMemcpyAsync(e->ids_dev, &token, 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemcpyAsync(e->want_dev, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    const uint32_t seq = (uint32_t)e->gen_seq;
+    if ((r = reserve_pages(e, seq, e->seqs[seq].len + 1)) || (r = embed_tokens(e, e->ids_dev, 1)) || (r = run_layers(e, seq, 1, e->seqs[seq].len))) return r;
+    e->seqs[seq].len += 1;
+    return head_rows(e, 1);
+}
+
+int lm_forward(nb200_engine *h, uint32_t token, uint32_t pos, uint32_t is_causal) {
+    LayeredEngine *e = self(h);
+    if (!is_causal) return fail(NB200_EINVAL, "this model family is causal only");
+    CK(cudaSetDevice(e->device));
+    int r;
+    if ((r = gen_seek(e, nullptr, pos)) || (r = gen_token(e, token))) return r;
+    CK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int lm_read_logits(nb200_engine *h, float *out) {
+    LayeredEngine *e = self(h);
+    if (!out) return fail(NB200_EINVAL, "null argument");
+    CK(cudaSetDevice(e->device));
+    CK(cudaMemcpyAsync(out, e->logits, (size_t)e->V * 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int mark_seen(LayeredEngine *e, const uint32_t *ids, uint32_t pos) {
+    CK(cudaMemsetAsync(e->seen, 0, e->V, e->stream));
+    if (!pos) return 0;
+    int r;
+    if ((r = check_tokens(e, ids, pos))) return r;
+    if (pos > e->max_tokens) return fail(NB200_EINVAL, "more ids than the engine's max_tokens");
+    CK(cudaMemcpyAsync(e->ids_dev + 8, ids, (size_t)pos * 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    k_mark<<<ew_grid(pos), 256, 0, e->stream>>>(e->seen, e->ids_dev + 8, pos);
+    CK(cudaGetLastError());
+    e->launches++;
+    return 0;
+}
+
+int lm_next_greedy(nb200_engine *h, const uint32_t *ids, uint32_t pos, int is_prefilling, float penalty, uint32_t *next) {
+    LayeredEngine *e = self(h);
+    if (!ids || !next) return fail(NB200_EINVAL, "null argument");
+    CK(cudaSetDevice(e->device));
+    int r;
+    if ((r = gen_seek(e, ids, pos)) || (r = gen_token(e, ids[pos]))) return r;
+    const float pen = is_prefilling ? 1.0f : penalty;
+    if (pen != 1.0f && (r = mark_seen(e, ids, pos))) return r;
+    PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, pen, 0};
+    if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
+    CK(cudaMemcpyAsync(e->tok_host, e->next_dev, 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    *next = is_prefilling ? ids[pos + 1] : *e->tok_host;
+    return 0;
+}
+
+int lm_next_sampled(nb200_engine *h, const uint32_t *ids, uint32_t pos, float penalty, float temperature, float top_p, float coin, uint32_t *next, uint32_t *top6) {
+    LayeredEngine *e = self(h);
+    if (!ids || !next) return fail(NB200_EINVAL, "null argument");
+    if (!(temperature > 0.0f)) return fail(NB200_EINVAL, "temperature must be > 0 (use nb200_next_greedy for 0)");
+    CK(cudaSetDevice(e->device));
+    if (!e->samp_ws) {
+        const size_t bytes = nb::sample_workspace_bytes(e->V, &e->samp_cub);
+        DM(e->samp_ws, bytes);
+        CK(cudaHostAlloc(&e->samp_host, 64, cudaHostAllocDefault));
+    }
+    int r;
+    if ((r = gen_seek(e, ids, pos)) || (r = gen_token(e, ids[pos]))) return r;
+    if (penalty != 1.0f) {      // k_pick applies the penalty to the logits in place; its greedy choice is not used
+        if ((r = mark_seen(e, ids, pos))) return r;
+        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, penalty, 0};
+        if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
+    }
+    uint32_t *out_dev = nullptr;
+    CK(nb::sample_top_p_launch(e->samp_ws, e->samp_cub, e->logits, e->V, temperature, top_p, coin, nullptr, &out_dev, e->stream));
+    e->launches += 3;
+    CK(cudaMemcpyAsync(e->samp_host, out_dev, 32, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    *next = e->samp_host[0];
+    if (top6) for (int i = 0; i < 6; i++) top6[i] = e->samp_host[1 + i];
+    return 0;
+}
+
+// prompt ids[0..n_prompt) -> greedy ids[n_prompt..n_total); positions 0..n_prompt-2 run as one prefill portion, the rest token by
+// token with the choice fed back on the device (no host round trip per token)
+int lm_decode_greedy(nb200_engine *h, uint32_t *ids, uint32_t n_prompt, uint32_t n_total, float penalty, float *prefill_ms, float *device_ms) {
+    LayeredEngine *e = self(h);
+    if (!ids) return fail(NB200_EINVAL, "null argument");
+    if (n_prompt < 1 || n_total < n_prompt || n_total > e->max_tokens + 1) return fail(NB200_EINVAL, "bad n_prompt/n_total");
+    int r;
+    if ((r = check_tokens(e, ids, n_prompt))) return r;
+    CK(cudaSetDevice(e->device));
+    if ((r = gen_reset(e))) return r;
+    const uint32_t seq = (uint32_t)e->gen_seq;
+    Seq &s = e->seqs[seq];
+    if ((r = reserve_pages(e, seq, n_total))) return r;
+    struct Events { cudaEvent_t ev[3] = {nullptr, nullptr, nullptr}; ~Events() { for (auto v : ev) if (v) cudaEventDestroy(v); } } evs;
+    for (auto &v : evs.ev) CK(cudaEventCreate(&v));
+    CK(cudaMemcpyAsync(e->ids_dev, ids, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemsetAsync(e->seen, 0, e->V, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    const uint32_t zero = 0;
+    CK(cudaMemcpyAsync(e->want_dev, &zero, 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaEventRecord(evs.ev[0], e->stream));
+    if (n_prompt > 1) {
+        if ((r = step_dev(e, seq, e->ids_dev, n_prompt - 1, nullptr, 0, nullptr))) return r;
+        if (penalty != 1.0f) { k_mark<<<ew_grid(n_prompt - 1), 256, 0, e->stream>>>(e->seen, e->ids_dev, n_prompt - 1); CK(cudaGetLastError()); e->launches++; }
+    }
+    CK(cudaEventRecord(evs.ev[1], e->stream));
+    const uint64_t before = e->launches;
+    for (uint32_t pos = n_prompt - 1; pos + 1 < n_total; pos++) {
+        if ((r = embed_tokens(e, e->ids_dev + pos, 1)) || (r = run_layers(e, seq, 1, pos)) || (r = head_rows(e, 1))) return r;
+        s.len = pos + 1;
+        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, pos, n_prompt, penalty, 1};
+        if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
+    }
+    if (n_total > n_prompt) e->launches_per_token = (uint32_t)((e->launches - before) / (n_total - n_prompt));
+    CK(cudaEventRecord(evs.ev[2], e->stream));
+    CK(cudaMemcpyAsync(ids, e->ids_dev, (size_t)n_total * 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    float a = 0, b = 0;
+    CK(cudaEventElapsedTime(&a, evs.ev[0], evs.ev[1]));
+    CK(cudaEventElapsedTime(&b, evs.ev[1], evs.ev[2]));
+    if (prefill_ms) *prefill_ms = a;
+    if (device_ms) *device_ms = b;
+    return 0;
+}
+
+int lm_get_config(const nb200_engine *h, nb200_config *c) {
+    const LayeredEngine *e = self(h);
+    memset(c, 0, sizeof *c);
+    c->arch = NB200_ARCH_LAYERED; c->quant = e->f32 ? 0x00u : 0x16u;      // 0x16: bfloat16 weights as stored
+    c->vocab_size = e->V; c->n_layer = (uint32_t)e->runs.size(); c->n_embd = e->E; c->max_seq_len = e->max_tokens; c->tp_size = 1;
+    c->reserved[0] = 0; c->reserved[3] = (uint32_t)e->layers.size(); c->reserved[4] = e->chunk_cap; c->reserved[5] = e->n_pages; c->reserved[6] = (uint32_t)e->free_pages.size();
+    return 0;
+}
+
+void lm_destroy(nb200_engine *h) {
+    LayeredEngine *e = self(h);
+    cudaSetDevice(e->device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    for (void *p : e->allocs) cudaFree(p);
+    if (e->tok_host) cudaFreeHost(e->tok_host);
+    if (e->samp_host) cudaFreeHost(e->samp_host);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+const nb::EngineOps kLayeredOps = {lm_destroy, lm_get_config, lm_forward, lm_read_logits, lm_next_greedy, lm_next_sampled, lm_decode_greedy,
+                                   lm_seq_open, lm_seq_close, lm_step, lm_read_residual, lm_step_timed};
+
+uint32_t env_u32(const char *name, uint32_t dflt) { const char *s = getenv(name); return (s && *s) ? (uint32_t)strtoul(s, nullptr, 10) : dflt; }
+
+int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
+    const nb::Json &cfg = dir->config;
+    const nb::Json *layers = cfg.get("layers");
+    double eps;
+    if (!u32_of(&cfg, "vocab", &e->V) || !u32_of(&cfg, "width", &e->E) || !layers || layers->t != nb::Json::Arr || layers->arr.empty() || !cfg.get("norm") || !cfg.get("norm")->number("eps", &eps))
+        return fail(NB200_EINVAL, "config.json needs vocab, width, norm.eps and a non-empty list \"layers\"");
+    if (!e->V || !e->E) return fail(NB200_EINVAL, "zero vocab or width");
+    e->eps = (float)eps;
+    const uint32_t E = e->E, NL = (uint32_t)layers->arr.size();
+    Loader ld{e, dir};
+    int r;
+    if ((r = ld.stacked({"embed"}, {e->V}, E, &e->embed)) || (r = ld.stacked({"head"}, {e->V}, E, &e->head)) || (r = ld.vec("final.norm", {}, &e->final_norm))) return r;
+    e->layers.resize(NL);
+    for (uint32_t i = 0; i < NL; i++) {
+        const nb::Json &lj = layers->arr[i];
+        Layer &L = e->layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
+        if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
+        if ((r = ld.vec(p + "norm1", {}, &L.norm1)) || (r = ld.vec(p + "shift", {E}, &L.shift))) return r;
+        if (type->str == "rglru") { L.type = MIX_RGLRU; r = load_rglru(ld, mixer, p + "mix.", &L, E); }
+        else if (type->str == "latent_attention") { L.type = MIX_LATENT_ATTN; r = load_latent_attn(ld, mixer, p + "mix.", &L, E); }
+        else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
+        if (r) return r;
+        if (lj.present("mlp")) {
+            if ((r = ld.vec(p + "norm2", {}, &L.norm2)) || (r = load_moe(ld, lj.get("mlp"), p + "mlp.", &L, E))) return r;
+        }
+    }
+    // order of the layer runs
+    uint32_t lo = 0, hi = 0, times = 1;
+    if (cfg.present("loop")) {
+        const nb::Json *lp = cfg.get("loop");
+        if (!u32_of(lp, "start", &lo) || !u32_of(lp, "stop", &hi) || !u32_of(lp, "times", &times) || lo > hi || hi > NL || times < 1) return fail(NB200_EINVAL, "loop needs 0 <= start <= stop <= layers and times >= 1");
+    }
+    for (uint32_t i = 0; i < lo; i++) { Run q; q.layer = i; e->runs.push_back(q); }
+    for (uint32_t p = 0; p < times; p++) for (uint32_t i = lo; i < hi; i++) { Run q; q.layer = i; q.add_embed = p > 0 && i == lo; e->runs.push_back(q); if (q.add_embed) e->keep_x0 = true; }
+    for (uint32_t i = hi; i < NL; i++) { Run q; q.layer = i; e->runs.push_back(q); }
+
+    // state manager: slots and pages
+    e->max_tokens = max_tokens;
+    e->max_seqs = std::max(1u, env_u32("NB200_MAX_SEQS", 8));
+    e->chunk_cap = std::max(1u, std::min(max_tokens, env_u32("NB200_CHUNK", 1024)));
+    e->n_pages = (max_tokens + kPage - 1) / kPage + e->max_seqs;
+    size_t off = 0;
+    for (Run &q : e->runs) {
+        const Layer &L = e->layers[q.layer];
+        q.st_prev = off; off += E;
+        if (L.type == MIX_RGLRU) { q.st_S = off; off += L.C; q.st_conv = off; off += (size_t)(L.taps - 1) * L.C; }
+        else { DM(q.cache, (size_t)e->n_pages * kPage * L.R * 4); }
+    }
+    e->slot_floats = (off + 3) & ~(size_t)3;
+    DM(e->state, (size_t)e->max_seqs * e->slot_floats * 4);
+    DM(e->state_bak, e->slot_floats * 4);
+    DM(e->table, (size_t)e->max_seqs * e->n_pages * 4);
+    CK(cudaMemset(e->table, 0, (size_t)e->max_seqs * e->n_pages * 4));
+    e->seqs.resize(e->max_seqs);
+    for (uint32_t p = e->n_pages; p > 0; p--) e->free_pages.push_back(p - 1);
+
+    // scratch for one chunk
+    const size_t T = e->chunk_cap;
+    uint32_t mC = 0, mZ = 0, mQR = 0, mQ = 0, mHR = 0, mOV = 0, mNE = 0, mTop = 0, mFF = 0, mSFF = 0;
+    for (const Layer &L : e->layers) {
+        if (L.type == MIX_RGLRU) mC = std::max(mC, L.C);
+        else { mZ = std::max(mZ, L.QR + L.R); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim); mHR = std::max(mHR, L.H * L.R); mOV = std::max(mOV, L.H * L.vdim); }
+        if (L.has_mlp) { mNE = std::max(mNE, L.NE); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
+    }
+    DM(e->x, T * E * 4); DM(e->hm, T * E * 4); DM(e->h2, T * E * 4); DM(e->d, T * E * 4);
+    if (e->keep_x0) DM(e->x0, T * E * 4);
+    if (mC) { DM(e->b_yx, T * 2 * mC * 4); DM(e->b_u, T * mC * 4); DM(e->b_g, T * 2 * mC * 4); DM(e->b_sy, T * mC * 4); }
+    if (mZ) {
+        DM(e->b_z, T * mZ * 4); DM(e->b_cq, T * mQR * 4); DM(e->b_q, T * mQ * 4); DM(e->b_qa, T * mHR * 4); DM(e->b_ol, T * mHR * 4); DM(e->b_ov, T * mOV * 4);
+        uint32_t mPart = 0, mR = 0;
+        for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.R); }
+        DM(e->b_part, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
+        const int smem = (int)(((size_t)kAttnWarps * mR + (size_t)kPage * (mR + 1)) * 4);
+        if (smem > 48 * 1024) {
+            CK(cudaFuncSetAttribute((const void *)k_latent_attn<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            CK(cudaFuncSetAttribute((const void *)k_latent_attn<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            CK(cudaFuncSetAttribute((const void *)k_latent_attn<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            CK(cudaFuncSetAttribute((const void *)k_latent_attn<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        }
+    }
+    if (mNE) {
+        DM(e->b_zr, T * mNE * 4); DM(e->b_idx, T * mTop * 4); DM(e->b_wt, T * mTop * 4); DM(e->b_slot, T * mTop * 4); DM(e->b_rows, T * mTop * 4);
+        DM(e->b_cnt, (size_t)mNE * 4); DM(e->b_off, ((size_t)mNE + 1) * 4); DM(e->b_fill, (size_t)mNE * 4);
+        CK(cudaMemset(e->b_cnt, 0, (size_t)mNE * 4));
+        DM(e->b_hb, T * mFF * 4); DM(e->b_eo, T * mTop * E * 4);
+        if (mSFF) { DM(e->b_sh, T * mSFF * 4); DM(e->b_so, T * E * 4); }
+    }
+    DM(e->b_xn, (size_t)kWantBatch * E * 4); DM(e->logits, (size_t)kWantBatch * e->V * 4);
+    DM(e->ids_dev, ((size_t)max_tokens + 16) * 4); DM(e->want_dev, kWantBatch * 4); DM(e->next_dev, 64); DM(e->seen, e->V);
+    CK(cudaMemset(e->ids_dev, 0, ((size_t)max_tokens + 16) * 4));
+    CK(cudaMemset(e->seen, 0, e->V));
+    if (env_u32("NB200_KEEP_RESIDUALS", 0)) DM(e->keep, e->runs.size() * T * E * 4);
+    CK(cudaHostAlloc(&e->tok_host, 64, cudaHostAllocDefault));
+    CK(cudaDeviceSynchronize());
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int nb_family_layered_create(nb200_engine **out, const nb::ModelDir *dir, uint32_t max_tokens, int device, uint32_t flags) {
+    CK(cudaSetDevice(device));
+    LayeredEngine *e = new LayeredEngine();
+    e->ops = &kLayeredOps;
+    e->device = device; e->f32 = (flags & NB200_FLAG_F32) != 0;
+    cudaDeviceProp prop;
+    cudaError_t ce = cudaGetDeviceProperties(&prop, device);
+    if (ce == cudaSuccess) { e->num_sms = prop.multiProcessorCount; ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking); }
+    int r = ce == cudaSuccess ? create(e, dir, max_tokens) : fail(NB200_ECUDA, "device setup failed: %s", cudaGetErrorString(ce));
+    if (r) { lm_destroy(reinterpret_cast<nb200_engine *>(e)); return r; }
+    *out = reinterpret_cast<nb200_engine *>(e);
+    return 0;
+}

@@ -1,0 +1,638 @@
+// layered_kernels.cuh -- device code of the layered runtime (layered.cu): models that are a list of typed layers, each a token
+// mixer plus an optional feed-forward, over an fp32 residual stream.  Every mechanism is a kernel (or a GEMM epilogue) of its own
+// with its constants as arguments, so a new design combines them by configuration:
+//
+//   matrix products      k_gemm_f32 (fp32 FMA tiles, the true-32-bit mode), k_gemm_bf16 (mma.sync m16n8k16, bf16 operands, fp32
+//                        accumulators: prefill), k_gemv (a warp per output row, weights streamed once: decode and portions of <= 4 tokens).
+//                        One argument block serves plain, grouped (block-diagonal gates, per-head absorb / value up-projection) and
+//                        routed (rows gathered per expert, group sizes read on the device) products; bias / gelu_tanh / sigmoid /
+//                        squared-relu epilogues.
+//   norms                k_norm_shift (RMS norm with ONE scalar gain, two gains of the same x at once, + token shift of the mixer's
+//                        input against the previous token's input, carried in the sequence state), k_latent_norm (vector-gain RMS norm
+//                        of the query latent and of the key/value latent, the latter written into the paged cache), k_final_norm
+//   recurrence           k_conv / k_conv_state (causal per-channel convolution with its taps-1 tail in the state), k_rglru_scan
+//                        (real-gated linear recurrent unit: a = exp(-c r softplus(lam)), S = a S + sqrt(1 - a^2) i u, fp32 state)
+//   attention            k_latent_attn (softmax attention of absorbed queries directly over cached latents: the latent is key AND
+//                        value, positions-free, causal; split over the keys for decode) + k_attn_merge
+//   mixture of experts   k_route (fp32 logits -> top-k, softmax over the chosen), k_route_scan, k_route_scatter (expert-sorted slots),
+//                        k_combine (weighted sum in choice order + shared expert + mixer output -> residual)
+//
+// What is fp32 here regardless of the weight type: the residual stream, every norm, router logits, attention scores / weights /
+// accumulators, gates, decays and the recurrent state.  bf16 enters only as a matrix-product operand.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace nb {
+namespace lm {
+
+constexpr uint32_t kPage = 32;            // tokens per cache page == keys per attention tile
+constexpr uint32_t kAttnWarps = 8;        // heads per attention block
+constexpr uint32_t kGemvMaxM = 4;         // rows a k_gemv launch handles per group
+
+enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4 };
+
+// C[r, c0 + n] = epi( sum_k A[arow(r), a0 + k] * W[g][n, k] + bias[g][n] )   for the rows r of group g
+//   rows of group g : [g_off[g], g_off[g+1])  when g_off is given (sizes known on the device only), else [0, M)
+//   arow(r)         : a_rows[r] when given (gather), else r
+//   a0 = (g % a_gmod) * a_gcols,  c0 = g * c_gcols,  W[g] = W + g * w_gstride,  bias[g] = bias + g * b_gstride
+struct GemmArgs {
+    const float *A; const void *W; float *C; const float *bias;
+    const uint32_t *g_off; const uint32_t *a_rows;
+    uint32_t M, N, K, lda, ldw, ldc;
+    uint32_t a_gmod, a_gcols, c_gcols, b_gstride;
+    uint64_t w_gstride;
+    uint32_t epi, split;      // EPI_GELU_SPLIT: gelu_tanh on columns n < split, bias only on the others
+    uint32_t round_a;         // k_gemv: round A to bf16 first (what the tensor-core kernel does to its operand)
+};
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.0f); }
+
+__device__ __forceinline__ float epilogue(float v, const GemmArgs &a, const float *bias, uint32_t n) {
+    if (bias) v += bias[n];
+    switch (a.epi) {
+        case EPI_GELU_SPLIT: return n < a.split ? gelu_tanh(v) : v;
+        case EPI_SIGMOID: return sigmoidf_(v);
+        case EPI_RELU2: { const float r = fmaxf(v, 0.0f); return r * r; }
+        default: return v;
+    }
+}
+
+struct GroupView { uint32_t r0, rows, a0, c0; const float *bias; uint64_t w0; };
+__device__ __forceinline__ GroupView group_view(const GemmArgs &a, uint32_t g) {
+    GroupView v;
+    v.r0 = a.g_off ? a.g_off[g] : 0u;
+    v.rows = a.g_off ? a.g_off[g + 1] - v.r0 : a.M;
+    v.a0 = (g % a.a_gmod) * a.a_gcols; v.c0 = g * a.c_gcols;
+    v.bias = a.bias ? a.bias + (size_t)g * a.b_gstride : nullptr;
+    v.w0 = (uint64_t)g * a.w_gstride;
+    return v;
+}
+
+__device__ __forceinline__ float wval(const float *w) { return *w; }
+__device__ __forceinline__ float wval(const __nv_bfloat16 *w) { return __bfloat162float(*w); }
+
+// ------------------------------------------------------------------------------------------------
+// fp32 tile product: 64 x 64 output tile, 16-deep k steps, 256 threads with a 4 x 4 micro-tile each; plain FMA in k order
+// ------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemm_f32(const GemmArgs a) {
+    const GroupView gv = group_view(a, blockIdx.z);
+    const uint32_t m0 = blockIdx.y * 64u, n0 = blockIdx.x * 64u;
+    if (m0 >= gv.rows) return;
+    __shared__ float As[16][64 + 4], Bs[16][64 + 4];
+    __shared__ uint32_t arow[64];
+    const uint32_t tid = threadIdx.x, ty = tid >> 4, tx = tid & 15u;
+    if (tid < 64) {
+        const uint32_t r = m0 + tid;
+        arow[tid] = r < gv.rows ? (a.a_rows ? a.a_rows[gv.r0 + r] : gv.r0 + r) : 0xffffffffu;
+    }
+    __syncthreads();
+    const WT *W = static_cast<const WT *>(a.W) + gv.w0;
+    float acc[4][4] = {};
+    const uint32_t lr = tid >> 2, lk = (tid & 3u) * 4u;       // this thread stages 4 consecutive k of one row, for A and for W
+    for (uint32_t k0 = 0; k0 < a.K; k0 += 16u) {
+        {
+            const uint32_t ar = arow[lr];
+            const float *src = a.A + (size_t)ar * a.lda + gv.a0 + k0 + lk;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; j++) As[lk + j][lr] = (ar != 0xffffffffu && k0 + lk + j < a.K) ? src[j] : 0.0f;
+            const uint32_t n = n0 + lr;
+            const WT *ws = W + (size_t)n * a.ldw + k0 + lk;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; j++) Bs[lk + j][lr] = (n < a.N && k0 + lk + j < a.K) ? wval(ws + j) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (uint32_t k = 0; k < 16; k++) {
+            float av[4], bv[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++) { av[i] = As[k][ty * 4 + i]; bv[i] = Bs[k][tx * 4 + i]; }
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++)
+#pragma unroll
+                for (uint32_t j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < 4; i++) {
+        const uint32_t r = m0 + ty * 4 + i;
+        if (r >= gv.rows) continue;
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j++) {
+            const uint32_t n = n0 + tx * 4 + j;
+            if (n < a.N) a.C[(size_t)(gv.r0 + r) * a.ldc + gv.c0 + n] = epilogue(acc[i][j], a, gv.bias, n);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// bf16 tensor-core tile product: 64 x 64 tile, 32-deep k steps, 4 warps (2 x 2, 32 x 32 each), mma.sync.m16n8k16 with fp32
+// accumulators.  A arrives as fp32 and is rounded to bf16 while it is staged; W is bf16 [n][k].  Two stages: the global loads
+// of step i+1 are in flight (registers) while step i multiplies.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) k_gemm_bf16(const GemmArgs a) {
+    const GroupView gv = group_view(a, blockIdx.z);
+    const uint32_t m0 = blockIdx.y * 64u, n0 = blockIdx.x * 64u;
+    if (m0 >= gv.rows) return;
+    constexpr uint32_t LD = 40;                                  // 32 + 8 bf16: fragment loads hit 32 different banks
+    __shared__ __align__(16) __nv_bfloat16 As[64 * LD], Bs[64 * LD];
+    __shared__ uint32_t arow[64];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t wm = (warp >> 1) * 32u, wn = (warp & 1u) * 32u;
+    if (tid < 64) {
+        const uint32_t r = m0 + tid;
+        arow[tid] = r < gv.rows ? (a.a_rows ? a.a_rows[gv.r0 + r] : gv.r0 + r) : 0xffffffffu;
+    }
+    __syncthreads();
+    const __nv_bfloat16 *W = static_cast<const __nv_bfloat16 *>(a.W) + gv.w0;
+    // staging: thread -> row tid/2, 16 consecutive k starting at (tid%2)*16, for A and for W
+    const uint32_t lr = tid >> 1, lk = (tid & 1u) * 16u;
+    const uint32_t ar = arow[lr];
+    const float *asrc = a.A + (size_t)(ar == 0xffffffffu ? 0 : ar) * a.lda + gv.a0;
+    const uint32_t wn_row = n0 + lr;
+    const __nv_bfloat16 *wsrc = W + (size_t)(wn_row < a.N ? wn_row : 0) * a.ldw;
+    const bool a_vec = ((reinterpret_cast<uintptr_t>(asrc) & 15u) == 0) && (a.lda % 4u == 0);
+    const bool w_vec = ((reinterpret_cast<uintptr_t>(wsrc) & 15u) == 0) && (a.ldw % 8u == 0);
+    float ra[16]; __align__(16) __nv_bfloat16 rw[16];
+    auto fetch = [&](uint32_t k0) {
+        const uint32_t kb = k0 + lk;
+        if (ar != 0xffffffffu && a_vec && kb + 16u <= a.K) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; j++) { const float4 v = *reinterpret_cast<const float4 *>(asrc + kb + 4 * j); ra[4 * j] = v.x; ra[4 * j + 1] = v.y; ra[4 * j + 2] = v.z; ra[4 * j + 3] = v.w; }
+        } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j++) ra[j] = (ar != 0xffffffffu && kb + j < a.K) ? asrc[kb + j] : 0.0f;
+        }
+        if (wn_row < a.N && w_vec && kb + 16u <= a.K) {
+            *reinterpret_cast<uint4 *>(rw) = *reinterpret_cast<const uint4 *>(wsrc + kb);
+            *reinterpret_cast<uint4 *>(rw + 8) = *reinterpret_cast<const uint4 *>(wsrc + kb + 8);
+        } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j++) rw[j] = (wn_row < a.N && kb + j < a.K) ? wsrc[kb + j] : __float2bfloat16(0.0f);
+        }
+    };
+    auto stage = [&]() {
+        __nv_bfloat16 *da = As + lr * LD + lk, *db = Bs + lr * LD + lk;
+#pragma unroll
+        for (uint32_t j = 0; j < 16; j += 2) {
+            *reinterpret_cast<__nv_bfloat162 *>(da + j) = __floats2bfloat162_rn(ra[j], ra[j + 1]);
+            *reinterpret_cast<__nv_bfloat162 *>(db + j) = __halves2bfloat162(rw[j], rw[j + 1]);
+        }
+    };
+    float acc[2][4][4] = {};
+    fetch(0);
+    for (uint32_t k0 = 0; k0 < a.K; k0 += 32u) {
+        stage();
+        __syncthreads();
+        if (k0 + 32u < a.K) fetch(k0 + 32u);
+#pragma unroll
+        for (uint32_t kk = 0; kk < 32; kk += 16) {
+            uint32_t af[2][4], bf[4][2];
+#pragma unroll
+            for (uint32_t i = 0; i < 2; i++) {
+                const __nv_bfloat16 *p = As + (wm + i * 16 + g) * LD + kk + 2 * t;
+                af[i][0] = *reinterpret_cast<const uint32_t *>(p);
+                af[i][1] = *reinterpret_cast<const uint32_t *>(p + 8 * LD);
+                af[i][2] = *reinterpret_cast<const uint32_t *>(p + 8);
+                af[i][3] = *reinterpret_cast<const uint32_t *>(p + 8 * LD + 8);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 4; j++) {
+                const __nv_bfloat16 *p = Bs + (wn + j * 8 + g) * LD + kk + 2 * t;
+                bf[j][0] = *reinterpret_cast<const uint32_t *>(p);
+                bf[j][1] = *reinterpret_cast<const uint32_t *>(p + 8);
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < 2; i++)
+#pragma unroll
+                for (uint32_t j = 0; j < 4; j++) mma_bf16(acc[i][j], af[i], bf[j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < 2; i++)
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j++)
+#pragma unroll
+            for (uint32_t q = 0; q < 4; q++) {
+                const uint32_t r = m0 + wm + i * 16 + g + (q >> 1) * 8, n = n0 + wn + j * 8 + 2 * t + (q & 1u);
+                if (r < gv.rows && n < a.N) a.C[(size_t)(gv.r0 + r) * a.ldc + gv.c0 + n] = epilogue(acc[i][j][q], a, gv.bias, n);
+            }
+}
+
+// ------------------------------------------------------------------------------------------------
+// matrix-vector product for up to kGemvMaxM rows per group: one warp per output column, lanes stride over k with 16-byte weight
+// loads; the weight vector is read once and used for every row.  grid = (column blocks, groups).
+// ------------------------------------------------------------------------------------------------
+template <typename WT> struct WVec;
+template <> struct WVec<float> {
+    static constexpr uint32_t N = 4;
+    static __device__ __forceinline__ void load(const float *p, float (&w)[N]) { const float4 v = __ldg(reinterpret_cast<const float4 *>(p)); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+};
+template <> struct WVec<__nv_bfloat16> {
+    static constexpr uint32_t N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&w)[N]) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(u[i] << 16); w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+    }
+};
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
+    const GroupView gv = group_view(a, blockIdx.y);
+    if (gv.rows == 0) return;
+    const uint32_t rows = gv.rows < kGemvMaxM ? gv.rows : kGemvMaxM;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = gridDim.x * (blockDim.x >> 5);
+    const WT *W = static_cast<const WT *>(a.W) + gv.w0;
+    const float *ap[kGemvMaxM];
+    bool vec = (a.ldw % WVec<WT>::N == 0) && ((reinterpret_cast<uintptr_t>(W) & 15u) == 0);
+#pragma unroll
+    for (uint32_t i = 0; i < kGemvMaxM; i++) {
+        const uint32_t r = gv.r0 + (i < rows ? i : 0);
+        ap[i] = a.A + (size_t)(a.a_rows ? a.a_rows[r] : r) * a.lda + gv.a0;
+        vec = vec && ((reinterpret_cast<uintptr_t>(ap[i]) & 15u) == 0);
+    }
+    constexpr uint32_t VN = WVec<WT>::N;
+    const uint32_t kvec = vec ? (a.K / VN) * VN : 0u;
+    for (uint32_t n = warp0; n < a.N; n += nwarps) {
+        const WT *wr = W + (size_t)n * a.ldw;
+        float acc[kGemvMaxM] = {};
+        for (uint32_t k = lane * VN; k < kvec; k += 32u * VN) {
+            float w[VN];
+            WVec<WT>::load(wr + k, w);
+#pragma unroll
+            for (uint32_t i = 0; i < kGemvMaxM; i++) {
+                if (i < rows) {
+#pragma unroll
+                    for (uint32_t j = 0; j < VN; j += 4) {
+                        const float4 x = *reinterpret_cast<const float4 *>(ap[i] + k + j);
+                        if (a.round_a) {
+                            acc[i] = fmaf(w[j], round_bf16(x.x), acc[i]); acc[i] = fmaf(w[j + 1], round_bf16(x.y), acc[i]);
+                            acc[i] = fmaf(w[j + 2], round_bf16(x.z), acc[i]); acc[i] = fmaf(w[j + 3], round_bf16(x.w), acc[i]);
+                        } else {
+                            acc[i] = fmaf(w[j], x.x, acc[i]); acc[i] = fmaf(w[j + 1], x.y, acc[i]);
+                            acc[i] = fmaf(w[j + 2], x.z, acc[i]); acc[i] = fmaf(w[j + 3], x.w, acc[i]);
+                        }
+                    }
+                }
+            }
+        }
+        for (uint32_t k = kvec + lane; k < a.K; k += 32u) {
+            const float w = wval(wr + k);
+#pragma unroll
+            for (uint32_t i = 0; i < kGemvMaxM; i++)
+                if (i < rows) { const float x = ap[i][k]; acc[i] = fmaf(w, a.round_a ? round_bf16(x) : x, acc[i]); }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kGemvMaxM; i++) {
+            float v = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && i < rows) a.C[(size_t)(gv.r0 + i) * a.ldc + gv.c0 + n] = epilogue(v, a, gv.bias, n);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// block-wide sum (blockDim.x a multiple of 32, <= 1024); every thread gets the result
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.0f;
+    for (uint32_t w = 0; w < (blockDim.x >> 5); w++) s += red[w];
+    return s;
+}
+
+// x[t] = embed[token]; x0 keeps a copy when a later pass adds the embedding output again
+template <typename WT>
+__global__ void k_embed(const uint32_t *__restrict__ tokens, const WT *__restrict__ embed, float *__restrict__ x, float *__restrict__ x0, uint32_t E) {
+    const uint32_t t = blockIdx.x;
+    const WT *src = embed + (size_t)tokens[t] * E;
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
+        const float v = wval(src + i);
+        x[(size_t)t * E + i] = v;
+        if (x0) x0[(size_t)t * E + i] = v;
+    }
+}
+
+__global__ void k_add(float *__restrict__ x, const float *__restrict__ y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] += y[i];
+}
+
+// Scalar-gain RMS norm of x with two gains at once (mixer input, feed-forward input) and the token shift of the mixer input:
+//   n1[t] = x[t] / rms(x[t]) * g1,  hm[t] = n1[t] + (n1[t-1] - n1[t]) * mu,  n1[-1] = the state (zeros at the start of a sequence),
+//   h2[t] = x[t] / rms(x[t]) * g2.   The state becomes n1[T-1].
+// Block b handles token b; block 0 also handles the LAST token after token 0, so the one reader and the one writer of the state
+// are the same block, in that order.
+struct NormShiftArgs {
+    const float *x; const float *g1, *g2, *mu; float *state; float *hm, *h2;
+    uint32_t T, E; float eps;
+};
+__device__ __forceinline__ void norm_shift_token(const NormShiftArgs &a, uint32_t t, float *red) {
+    const float *xt = a.x + (size_t)t * a.E, *xp = t ? xt - a.E : nullptr;
+    float s = 0.0f, sp = 0.0f;
+    for (uint32_t i = threadIdx.x; i < a.E; i += blockDim.x) { const float v = xt[i]; s = fmaf(v, v, s); if (xp) { const float u = xp[i]; sp = fmaf(u, u, sp); } }
+    s = block_sum(s, red);
+    sp = block_sum(sp, red);
+    const float rinv = 1.0f / sqrtf(s / (float)a.E + a.eps), rinvp = 1.0f / sqrtf(sp / (float)a.E + a.eps);
+    const float g1 = *a.g1, g2 = a.g2 ? *a.g2 : 0.0f;
+    for (uint32_t i = threadIdx.x; i < a.E; i += blockDim.x) {
+        const float u = xt[i] * rinv;
+        const float n1 = u * g1;
+        const float prev = xp ? xp[i] * rinvp * g1 : a.state[i];
+        a.hm[(size_t)t * a.E + i] = a.mu ? n1 + (prev - n1) * a.mu[i] : n1;
+        if (a.h2) a.h2[(size_t)t * a.E + i] = u * g2;
+        if (t + 1 == a.T) a.state[i] = n1;
+    }
+}
+__global__ void __launch_bounds__(256) k_norm_shift(const NormShiftArgs a) {
+    __shared__ float red[32];
+    norm_shift_token(a, blockIdx.x, red);
+    if (blockIdx.x == 0 && a.T > 1) { __syncthreads(); norm_shift_token(a, a.T - 1, red); }
+}
+
+// causal per-channel convolution: u[t,c] = b[c] + sum_j taps[c,j] * v[t - (K-1-j), c]; inputs before this portion come from the
+// state (the last K-1 inputs of the sequence so far, oldest first; zeros at the start)
+struct ConvArgs { const float *v; uint32_t ldv; const float *taps, *bias; float *state; float *u; uint32_t T, C, K; };
+__global__ void k_conv(const ConvArgs a) {
+    const size_t total = (size_t)a.T * a.C;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / a.C), c = (uint32_t)(i % a.C);
+        float s = a.bias[c];
+        for (uint32_t j = 0; j < a.K; j++) {
+            const int64_t src = (int64_t)t - (int64_t)(a.K - 1 - j);
+            const float v = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)((int64_t)(a.K - 1) + src) * a.C + c];
+            s = fmaf(a.taps[(size_t)c * a.K + j], v, s);
+        }
+        a.u[i] = s;
+    }
+}
+__global__ void k_conv_state(const ConvArgs a) {     // after k_conv: the tail becomes the last K-1 inputs, this portion included
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    for (uint32_t j = 0; j + 1 < a.K; j++) {
+        const int64_t src = (int64_t)a.T - (int64_t)(a.K - 1) + j;
+        a.state[(size_t)j * a.C + c] = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)(j + a.T) * a.C + c];
+    }
+}
+
+// real-gated linear recurrent unit, one thread per channel, tokens in order:
+//   a = exp(-c_decay * r * softplus(lam)),  S <- a S + sqrt(1 - a^2) * (i * u),  out = S * y
+struct ScanArgs { const float *gates; uint32_t ldg; const float *u; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C; float c_decay; };
+__global__ void k_rglru_scan(const ScanArgs a) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const float sp = softplusf_(a.lam[c]);
+    float S = a.S[c];
+    for (uint32_t t = 0; t < a.T; t++) {
+        const float r = a.gates[(size_t)t * a.ldg + c], i = a.gates[(size_t)t * a.ldg + a.C + c];
+        const float la = -a.c_decay * r * sp;
+        const float av = expf(la);
+        S = av * S + sqrtf(1.0f - av * av) * (i * a.u[(size_t)t * a.C + c]);
+        a.out[(size_t)t * a.C + c] = S * a.y[(size_t)t * a.ldy + c];
+    }
+    a.S[c] = S;
+}
+
+// vector-gain RMS norms of the two latents of one token: z = [query latent | key/value latent]; the query latent goes to cq, the
+// key/value latent into the sequence's cache page of position pos0 + t
+struct LatentNormArgs { const float *z; uint32_t ldz; const float *wq, *wkv; float *cq; float *cache; const uint32_t *table; uint32_t QR, R, pos0; float eps; };
+__global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
+    __shared__ float red[32];
+    const uint32_t t = blockIdx.x;
+    const float *z = a.z + (size_t)t * a.ldz;
+    float s = 0.0f, s2 = 0.0f;
+    for (uint32_t i = threadIdx.x; i < a.QR; i += blockDim.x) s = fmaf(z[i], z[i], s);
+    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) s2 = fmaf(z[a.QR + i], z[a.QR + i], s2);
+    s = block_sum(s, red);
+    s2 = block_sum(s2, red);
+    const float rq = 1.0f / sqrtf(s / (float)a.QR + a.eps), rk = 1.0f / sqrtf(s2 / (float)a.R + a.eps);
+    for (uint32_t i = threadIdx.x; i < a.QR; i += blockDim.x) a.cq[(size_t)t * a.QR + i] = z[i] * rq * a.wq[i];
+    const uint32_t pos = a.pos0 + t;
+    float *row = a.cache + ((size_t)a.table[pos / kPage] * kPage + pos % kPage) * a.R;
+    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) row[i] = z[a.QR + i] * rk * a.wkv[i];
+}
+
+// Softmax attention over cached latents.  qa[t][h][:] is head h's query already multiplied into latent space (q_h^T W_uk,h), so
+// score(t, j) = scale * qa[t][h] . c_j and the head's output in latent space is sum_j p_j c_j (multiplied by W_uv,h afterwards):
+// the latent row is key and value at once and is read once for all heads of a block.  Causal: keys 0 .. pos0 + t.
+// grid = (tokens, key splits, head groups of kAttnWarps); one warp per head; lanes = keys for the scores, = latent columns for the
+// weighted sum; online softmax in fp32.  With one split the normalised result is written; otherwise partial (o, m, l) triples.
+struct AttnArgs {
+    const float *qa; const float *cache; const uint32_t *table; float *out; float *part;
+    uint32_t T, H, R, pos0, nsplit; float scale;
+};
+template <int RCH>
+__global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
+    extern __shared__ float sm[];
+    const uint32_t t = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = h0 + warp;
+    const uint32_t R = a.R, LDC = R + 1u;
+    float *q_s = sm;                         // [kAttnWarps][R]
+    float *c_s = sm + kAttnWarps * R;        // [kPage][R + 1]
+    const uint32_t nkeys = a.pos0 + t + 1u, tiles = (nkeys + kPage - 1u) / kPage;
+    const uint32_t tps = (tiles + a.nsplit - 1u) / a.nsplit;
+    const uint32_t tile_lo = split * tps, tile_hi = min(tiles, tile_lo + tps);
+    for (uint32_t i = threadIdx.x; i < kAttnWarps * R; i += blockDim.x) {
+        const uint32_t hh = h0 + i / R;
+        q_s[i] = hh < a.H ? a.qa[((size_t)t * a.H + hh) * R + i % R] : 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f, o[RCH];
+#pragma unroll
+    for (int c = 0; c < RCH; c++) o[c] = 0.0f;
+    const float *qh = q_s + warp * R;
+    for (uint32_t tile = tile_lo; tile < tile_hi; tile++) {
+        __syncthreads();
+        const float *src = a.cache + (size_t)a.table[tile] * kPage * R;
+        const uint32_t nk = min(kPage, nkeys - tile * kPage);
+        for (uint32_t i = threadIdx.x; i < nk * R; i += blockDim.x) c_s[(i / R) * LDC + i % R] = src[i];
+        __syncthreads();
+        if (h < a.H) {
+            float s = -INFINITY;
+            if (lane < nk) {
+                const float *cr = c_s + lane * LDC;
+                float d = 0.0f;
+                for (uint32_t r = 0; r < R; r++) d = fmaf(qh[r], cr[r], d);
+                s = d * a.scale;
+            }
+            float tm = s;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
+            const float mn = fmaxf(m, tm);
+            const float corr = expf(m - mn);
+            const float p = lane < nk ? expf(s - mn) : 0.0f;
+            float ps = p;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+            l = l * corr + ps;
+            m = mn;
+#pragma unroll
+            for (int c = 0; c < RCH; c++) o[c] *= corr;
+            for (uint32_t j = 0; j < nk; j++) {
+                const float pj = __shfl_sync(0xffffffffu, p, j);
+                const float *cr = c_s + j * LDC;
+#pragma unroll
+                for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) o[c] = fmaf(pj, cr[r], o[c]); }
+            }
+        }
+    }
+    if (h >= a.H) return;
+    if (a.nsplit == 1) {
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) a.out[((size_t)t * a.H + h) * R + r] = o[c] * inv; }
+    } else {
+        float *dst = a.part + (((size_t)t * a.nsplit + split) * a.H + h) * (R + 2u);
+#pragma unroll
+        for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) dst[r] = o[c]; }
+        if (lane == 0) { dst[R] = m; dst[R + 1] = l; }
+    }
+}
+// grid = (tokens, heads): out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys
+__global__ void k_attn_merge(const AttnArgs a) {
+    const uint32_t t = blockIdx.x, h = blockIdx.y, R = a.R;
+    const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
+    const size_t stride = (size_t)a.H * (R + 2u);
+    float M = -INFINITY;
+    for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) M = fmaxf(M, base[s * stride + R]);
+    float L = 0.0f;
+    for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) L += expf(base[s * stride + R] - M) * base[s * stride + R + 1];
+    for (uint32_t r = threadIdx.x; r < R; r += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) acc = fmaf(expf(base[s * stride + R] - M), base[s * stride + r], acc);
+        a.out[((size_t)t * a.H + h) * R + r] = acc / L;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// mixture of experts: routing
+// ------------------------------------------------------------------------------------------------
+// one thread per token: the `top` largest logits (ties: the lower expert index first), weights = softmax over the chosen logits;
+// counts[e] += 1 per choice
+struct RouteArgs { const float *z; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top; };
+__global__ void k_route(const RouteArgs a) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= a.T) return;
+    const float *z = a.z + (size_t)t * a.NE;
+    uint32_t *idx = a.idx + (size_t)t * a.top; float *wt = a.wt + (size_t)t * a.top;
+    for (uint32_t j = 0; j < a.top; j++) {
+        float best = -INFINITY; uint32_t bi = 0xffffffffu;
+        for (uint32_t e = 0; e < a.NE; e++) {
+            bool taken = false;
+            for (uint32_t q = 0; q < j; q++) taken = taken || idx[q] == e;
+            const float v = z[e];
+            if (!taken && (bi == 0xffffffffu || v > best)) { best = v; bi = e; }
+        }
+        idx[j] = bi; wt[j] = best;
+    }
+    const float mx = wt[0];
+    float s = 0.0f;
+    for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - mx); s += wt[j]; }
+    for (uint32_t j = 0; j < a.top; j++) { wt[j] /= s; atomicAdd(a.counts + idx[j], 1u); }
+}
+// one thread: off[e] = rows before expert e (off[NE] = total); clears the fill counters and the counts for the next use
+__global__ void k_route_scan(const RouteArgs a) {
+    if (threadIdx.x || blockIdx.x) return;
+    uint32_t s = 0;
+    for (uint32_t e = 0; e < a.NE; e++) { a.off[e] = s; s += a.counts[e]; a.counts[e] = 0; a.fill[e] = 0; }
+    a.off[a.NE] = s;
+}
+// slot[t][j] = row of (token t, choice j) in the expert-sorted order; rows[slot] = t
+__global__ void k_route_scatter(const RouteArgs a) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.T * a.top) return;
+    const uint32_t e = a.idx[i];
+    const uint32_t s = a.off[e] + atomicAdd(a.fill + e, 1u);
+    a.slot[i] = s; a.rows[s] = i / a.top;
+}
+
+// x[t] += d[t] + ( sum_j wt[t][j] * eo[slot[t][j]]  (+ shared[t]) ),  the sum in the order of the choices; keep (optional) gets x
+struct CombineArgs { float *x; const float *d; const float *eo; const uint32_t *slot; const float *wt; const float *shared; float *keep; uint32_t T, E, top; };
+__global__ void k_combine(const CombineArgs a) {
+    const size_t total = (size_t)a.T * a.E;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / a.E), c = (uint32_t)(i % a.E);
+        float delta = a.d[i];
+        if (a.eo) {
+            float f = 0.0f;
+            for (uint32_t j = 0; j < a.top; j++) f = fmaf(a.wt[(size_t)t * a.top + j], a.eo[(size_t)a.slot[(size_t)t * a.top + j] * a.E + c], f);
+            if (a.shared) f += a.shared[i];
+            delta += f;
+        }
+        const float v = a.x[i] + delta;
+        a.x[i] = v;
+        if (a.keep) a.keep[i] = v;
+    }
+}
+
+// scalar-gain RMS norm of the rows whose logits are asked for: out[i] = x[want[i]] / rms * g
+__global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x, const uint32_t *__restrict__ want, const float *__restrict__ g,
+                                                    float *__restrict__ out, uint32_t E, float eps) {
+    __shared__ float red[32];
+    const float *xt = x + (size_t)want[blockIdx.x] * E;
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) s = fmaf(xt[i], xt[i], s);
+    s = block_sum(s, red);
+    const float rinv = 1.0f / sqrtf(s / (float)E + eps) * 1.0f;
+    const float gv = *g;
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)blockIdx.x * E + i] = xt[i] * rinv * gv;
+}
+
+// greedy choice with the repetition penalty of the generation hosts: logits of ids seen before are divided (positive) or multiplied
+// (negative) by `penalty`; the lowest index wins ties.  One block.  ids[pos + 1] receives the choice unless that place is still
+// inside the prompt (pos + 1 < n_prompt).  penalised (optional) receives the logits after the penalty, for the sampler.
+struct PickArgs { float *logits; const uint8_t *seen; uint8_t *seen_rw; uint32_t *ids; uint32_t *next; uint32_t V, pos, n_prompt; float penalty; uint32_t advance; };
+__global__ void __launch_bounds__(1024) k_pick(const PickArgs a) {
+    __shared__ float bv[32]; __shared__ uint32_t bi[32];
+    float best = -INFINITY; uint32_t idx = 0xffffffffu;
+    for (uint32_t i = threadIdx.x; i < a.V; i += blockDim.x) {
+        float v = a.logits[i];
+        if (a.penalty != 1.0f && a.seen[i]) { v = v > 0.0f ? v / a.penalty : v * a.penalty; a.logits[i] = v; }
+        if (v > best || idx == 0xffffffffu) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31u) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint32_t w = 1; w < (blockDim.x >> 5); w++)
+            if (bi[w] != 0xffffffffu && (bi[0] == 0xffffffffu || bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0]))) { bv[0] = bv[w]; bi[0] = bi[w]; }
+        uint32_t nxt = bi[0];
+        if (a.advance) {
+            a.seen_rw[a.ids[a.pos]] = 1;
+            if (a.pos + 1 < a.n_prompt) nxt = a.ids[a.pos + 1]; else a.ids[a.pos + 1] = nxt;
+        }
+        *a.next = nxt;
+    }
+}
+__global__ void k_mark(uint8_t *seen, const uint32_t *ids, uint32_t n) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) seen[ids[i]] = 1;
+}
+
+}  // namespace lm
+}  // namespace nb

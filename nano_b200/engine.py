@@ -18,7 +18,8 @@ u32p = C.POINTER(C.c_uint32)
 u8p = C.POINTER(C.c_uint8)
 i8p = C.POINTER(C.c_int8)
 
-FLAG_EXACT, FLAG_NO_GRAPH, FLAG_NO_PDL, FLAG_NO_STREAM = 0x1, 0x2, 0x4, 0x10
+FLAG_EXACT, FLAG_NO_GRAPH, FLAG_NO_PDL, FLAG_NO_STREAM, FLAG_F32 = 0x1, 0x2, 0x4, 0x10, 0x20
+ARCH_LAYERED = 16
 F_X, F_XBA, F_HB, F_Q, F_LOGITS, F_KROW, F_VROW, F_ACT_I8, F_ACT_SCALE = 0, 2, 4, 6, 9, 13, 14, 20, 21
 
 EXPORTS = [
@@ -30,6 +31,7 @@ EXPORTS = [
     "nb200_op_q4k_quantize_blocks", "nb200_op_q4k_matvec_blocks",
     "nb200_lora_load", "nb200_lora_enable", "nb200_lora_unload",
     "nb200_engine_create_tp", "nb200_tp_export", "nb200_tp_attach_ipc", "nb200_tp_attach_local",
+    "nb200_engine_create_dir", "nb200_seq_open", "nb200_seq_close", "nb200_step", "nb200_step_timed", "nb200_read_residual",
 ]
 
 
@@ -46,14 +48,34 @@ class NB200Error(RuntimeError):
 _lib = None
 
 
-def lib():
+class _Sig:
+    """Sets argtypes / restype on the symbols a library has: the model-folder build (build.LAYERED_SO) carries a subset."""
+
+    def __init__(self, L):
+        self.__dict__["_L"] = L
+
+    def __getattr__(self, name):
+        L = self.__dict__["_L"]
+        return getattr(L, name) if hasattr(L, name) else _Missing()
+
+
+class _Missing:
+    argtypes = restype = None
+
+
+def lib(layered_ok: bool = False):
+    """The engine library.  layered_ok: a host that only serves model folders accepts the library that holds just those families
+    (built in seconds) when the full one has not been built."""
     global _lib
     if _lib is None:
         path = os.environ.get("NB200_ENGINE_SO", _build.ENGINE_SO)     # developer hook: the fine-trace build (tools/gpu_trace.py)
+        if not os.path.exists(path) and layered_ok and os.path.exists(_build.LAYERED_SO):
+            path = _build.LAYERED_SO
         if not os.path.exists(path):
             raise NB200Error(f"{path} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
                              "(nano_b200 has no CPU fallback)")
-        L = C.CDLL(path)
+        raw = C.CDLL(path)
+        L = _Sig(raw)
         L.nb200_last_error.restype = C.c_char_p
         L.nb200_engine_create.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_uint64, C.c_uint32, C.c_int, C.c_uint32]
         L.nb200_engine_create_tp.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_uint64, C.c_uint32, C.c_int, C.c_uint32,
@@ -88,13 +110,19 @@ def lib():
         L.nb200_op_q4k_matvec.argtypes = [f32p, f32p, u8p, C.c_uint32, C.c_uint32]
         L.nb200_op_q4k_quantize_blocks.argtypes = [u8p, f32p, C.c_uint64]
         L.nb200_op_q4k_matvec_blocks.argtypes = [f32p, u8p, u8p, C.c_uint32, C.c_uint32]
+        L.nb200_engine_create_dir.argtypes = [C.POINTER(C.c_void_p), C.c_char_p, C.c_uint32, C.c_int, C.c_uint32]
+        L.nb200_seq_open.argtypes = [C.c_void_p, u32p]
+        L.nb200_seq_close.argtypes = [C.c_void_p, C.c_uint32]
+        L.nb200_step.argtypes = [C.c_void_p, C.c_uint32, u32p, C.c_uint32, u32p, C.c_uint32, f32p]
+        L.nb200_step_timed.argtypes = [C.c_void_p, C.c_uint32, u32p, C.c_uint32, C.c_uint32, f32p]
+        L.nb200_read_residual.argtypes = [C.c_void_p, C.c_uint32, f32p, C.c_uint32]
         L.nb200_lora_load.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
         L.nb200_lora_enable.argtypes = [C.c_void_p, C.c_int]
         L.nb200_lora_unload.argtypes = [C.c_void_p]
         L.nb200_host_expf_ref.restype = C.c_float
         L.nb200_host_expf_ref.argtypes = [C.c_float]
         L.nb200_host_expf_ref_array.argtypes = [f32p, f32p, C.c_uint64]
-        _lib = L
+        _lib = raw
     return _lib
 
 
@@ -116,12 +144,18 @@ class Engine:
 
     def __init__(self, model, max_seq: int, device: int = 0, flags: int = 0, tp: Optional[Tuple[int, int]] = None):
         """tp=(rank, size) creates one rank of a tensor-parallel group; attach it (tp_attach_ipc / TpGroup) before use."""
-        L = lib()
+        L = lib(layered_ok=isinstance(model, (str, os.PathLike)) and os.path.isdir(model))
+        self.h = C.c_void_p()
+        if isinstance(model, (str, os.PathLike)) and os.path.isdir(model):
+            # a model folder (config.json + model.safetensors): the library's registry picks the family; max_seq = token capacity
+            assert tp is None, "model folders run on one GPU"
+            _check(L.nb200_engine_create_dir(C.byref(self.h), os.fsencode(model), int(max_seq), device, flags))
+            self._refresh()
+            return
         if isinstance(model, (str, os.PathLike)):
             image = np.fromfile(model, dtype=np.uint8)
         else:
             image = np.frombuffer(bytes(model), dtype=np.uint8)
-        self.h = C.c_void_p()
         if tp is None:
             _check(L.nb200_engine_create(C.byref(self.h), image.ctypes.data, image.size, max_seq, device, flags))
         else:
@@ -142,6 +176,40 @@ class Engine:
         # creation-time calibration of the two fast paths (large one-GPU Q80 engines): us per token of each, None when not measured
         self.calibration = ({"streaming_us_per_token": int(cfg.reserved[1]), "multikernel_us_per_token": int(cfg.reserved[2])}
                             if int(cfg.reserved[1]) and int(cfg.reserved[2]) else None)
+
+    # ---- sequences (model folders): cache pages + a state slot per live request ----
+    def seq_open(self) -> int:
+        s = C.c_uint32(0)
+        _check(lib().nb200_seq_open(self.h, C.byref(s)))
+        return int(s.value)
+
+    def seq_close(self, seq: int) -> None:
+        _check(lib().nb200_seq_close(self.h, int(seq)))
+
+    def step(self, seq: int, tokens, want=()) -> np.ndarray:
+        """Runs the next tokens of `seq`; returns the logits [len(want), vocab] at the places `want` (indices into tokens)."""
+        t = np.ascontiguousarray(tokens, np.uint32); w = np.ascontiguousarray(sorted(want), np.uint32)
+        out = np.empty((w.size, self.vocab), np.float32)
+        _check(lib().nb200_step(self.h, int(seq), _p(t, u32p), t.size, _p(w, u32p) if w.size else None, w.size,
+                                _p(out, f32p) if w.size else None))
+        return out
+
+    def step_timed(self, seq: int, tokens, reps: int) -> float:
+        """Mean device milliseconds of running `tokens` from the sequence's present state (the state is restored between runs)."""
+        t = np.ascontiguousarray(tokens, np.uint32); ms = C.c_float(0)
+        _check(lib().nb200_step_timed(self.h, int(seq), _p(t, u32p), t.size, int(reps), C.byref(ms)))
+        return float(ms.value)
+
+    def read_residual(self, run: int, tokens: int) -> np.ndarray:
+        out = np.empty((tokens, self.n_embd), np.float32)
+        _check(lib().nb200_read_residual(self.h, int(run), _p(out, f32p), out.size))
+        return out
+
+    @property
+    def free_pages(self) -> int:
+        cfg = Config()
+        _check(lib().nb200_get_config(self.h, C.byref(cfg)))
+        return int(cfg.reserved[6])
 
     # ---- LoRA plug-in ----
     def lora_load(self, image: bytes) -> None:
