@@ -1,0 +1,116 @@
+"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra models for the
+benchmarks and tests.  The reader the engine uses is native (csrc/modeldir.cu); nothing here is on the compute path.
+
+A safetensors file is an 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets) and
+the tensor bytes.
+"""
+from __future__ import annotations
+
+import json
+import os
+import struct
+from typing import Dict
+
+import numpy as np
+
+
+def to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    """fp32 -> bfloat16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """The fp32 values a bfloat16 file would hold."""
+    return (to_bf16_bits(a).astype(np.uint32) << 16).view(np.float32).reshape(np.shape(a))
+
+
+def write_safetensors(path: str, tensors: Dict[str, np.ndarray], bf16: bool = True) -> None:
+    header, blobs, off = {}, [], 0
+    for name, arr in tensors.items():
+        arr = np.asarray(arr)
+        if arr.dtype.kind == "i":
+            data, dt = np.ascontiguousarray(arr, "<i4").tobytes(), "I32"
+        elif bf16:
+            data, dt = to_bf16_bits(arr).astype("<u2").tobytes(), "BF16"
+        else:
+            data, dt = np.ascontiguousarray(arr, "<f4").tobytes(), "F32"
+        header[name] = {"dtype": dt, "shape": list(arr.shape), "data_offsets": [off, off + len(data)]}
+        blobs.append(data)
+        off += len(data)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def write_model_dir(path: str, config: dict, tensors: Dict[str, np.ndarray], bf16: bool = True) -> str:
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(config, f, indent=1)
+    write_safetensors(os.path.join(path, "model.safetensors"), tensors, bf16)
+    return path
+
+
+def famudra_config(vocab: int, width: int, layers, loop=None, eps: float = 1e-5) -> dict:
+    """layers: list of ("rglru", {width, blocks, conv}, mlp) / ("latent_attention", {heads, dim, vdim, kv_rank, q_rank, scale}, mlp);
+    mlp: None or {"experts": n, "top": k, "ff": f, "shared_ff": s or None}."""
+    out = []
+    for kind, mixer, mlp in layers:
+        m = None
+        if mlp:
+            m = {"kind": "moe", "router": {"experts": mlp["experts"], "top": mlp["top"]}, "expert": {"ff": mlp["ff"]},
+                 "shared": {"ff": mlp["shared_ff"]} if mlp.get("shared_ff") else None}
+        out.append({"type": kind, "mixer": dict(mixer), "mlp": m})
+    cfg = {"architecture": "Famudra", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": out}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def famudra_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, np.ndarray]:
+    """Random weights (bfloat16-representable fp32 arrays) for a Famudra config: projections ~ N(0, gain^2 / fan_in)."""
+    rng = np.random.default_rng(seed)
+    E, V = config["width"], config["vocab"]
+
+    def lin(o, i, g=1.0):
+        return bf16_round((rng.standard_normal((o, i), dtype=np.float32) * (gain * g / np.sqrt(i))).astype(np.float32))
+
+    def vecn(n, lo, hi):
+        return bf16_round(rng.uniform(lo, hi, size=n).astype(np.float32))
+
+    t = {"embed": bf16_round(rng.standard_normal((V, E), dtype=np.float32)), "head": lin(V, E), "final.norm": vecn((), 0.8, 1.2)}
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        t[p + "norm1"] = vecn((), 0.8, 1.2)
+        t[p + "shift"] = vecn(E, 0.0, 1.0)
+        m = L["mixer"]
+        if L["type"] == "rglru":
+            C, B, K = m["width"], m["blocks"], m["conv"]
+            bs = C // B
+            t[p + "mix.y"] = lin(C, E); t[p + "mix.y.b"] = vecn(C, -0.2, 0.2)
+            t[p + "mix.x"] = lin(C, E); t[p + "mix.x.b"] = vecn(C, -0.2, 0.2)
+            t[p + "mix.conv"] = vecn((C, K), -0.6, 0.6); t[p + "mix.conv.b"] = vecn(C, -0.1, 0.1)
+            t[p + "mix.ra"] = np.stack([lin(bs, bs) for _ in range(B)]); t[p + "mix.ra.b"] = vecn((B, bs), -0.5, 0.5)
+            t[p + "mix.ri"] = np.stack([lin(bs, bs) for _ in range(B)]); t[p + "mix.ri.b"] = vecn((B, bs), -0.5, 0.5)
+            t[p + "mix.lam"] = vecn(C, -4.0, 0.5)
+            t[p + "mix.o"] = lin(E, C)
+        else:
+            H, D, VD, R, QR = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"] = lin(QR, E); t[p + "mix.dq.norm"] = vecn(QR, 0.7, 1.3)
+            t[p + "mix.uq"] = lin(H * D, QR)
+            t[p + "mix.dkv"] = lin(R, E); t[p + "mix.dkv.norm"] = vecn(R, 0.7, 1.3)
+            t[p + "mix.uk"] = lin(H * D, R); t[p + "mix.uv"] = lin(H * VD, R)
+            t[p + "mix.o"] = lin(E, H * VD)
+        f = L.get("mlp")
+        if f:
+            t[p + "norm2"] = vecn((), 0.8, 1.2)
+            t[p + "mlp.router"] = lin(f["router"]["experts"], E, 2.0)
+            for e in range(f["router"]["experts"]):
+                t[p + f"mlp.e{e}.up"] = lin(f["expert"]["ff"], E); t[p + f"mlp.e{e}.down"] = lin(E, f["expert"]["ff"])
+            if f.get("shared"):
+                t[p + "mlp.shared.up"] = lin(f["shared"]["ff"], E); t[p + "mlp.shared.down"] = lin(E, f["shared"]["ff"])
+    return t
