@@ -479,6 +479,112 @@ def tp_block(E, rank, world, local, dist):
     return out
 
 
+
+# --------------------------------------------------------------------------------------------------
+# --design famudra: prefill and decode throughput of the layered family at layer sizes of real models (random weights), beside the
+# closest model the engine had before it -- a Qwen3-architecture Q80 model file of the same width and depth.  Not the default
+# workload: the headline line and its contract are untouched.
+# --------------------------------------------------------------------------------------------------
+FAMUDRA_SIZES = {
+    # name: (width, layers, recurrent width / blocks, heads, dim, vdim, kv_rank, q_rank, experts, top, expert ff, shared ff, peer hidden)
+    "w1024": (1024, 8, 1024, 8, 16, 64, 64, 256, 512, 16, 2, 512, 1024, 3072),
+    "w2048": (2048, 8, 2048, 16, 16, 128, 128, 512, 768, 16, 2, 1024, 2048, 6144),
+}
+FAMUDRA_VOCAB = 32000
+
+
+def famudra_model(name):
+    from nano_b200 import modeldir as md
+    E_, L, C, B, H, D, VD, R, QR, NE, top, ff, sff, _peer = FAMUDRA_SIZES[name]
+    mlp = {"experts": NE, "top": top, "ff": ff, "shared_ff": sff}
+    layers = [("rglru", {"width": C, "blocks": B, "conv": 4}, mlp) if i % 2 == 0 else
+              ("latent_attention", {"heads": H, "dim": D, "vdim": VD, "kv_rank": R, "q_rank": QR, "scale": D ** -0.5}, mlp) for i in range(L)]
+    cfg = md.famudra_config(FAMUDRA_VOCAB, E_, layers)
+    path = os.path.join(os.environ.get("NB200_MODEL_CACHE", "/tmp/nb200_models"), f"famudra-{name}")
+    if not os.path.exists(os.path.join(path, "model.safetensors")):
+        md.write_model_dir(path + ".part", cfg, md.famudra_random(cfg, 0))
+        os.replace(path + ".part", path)
+    return path, cfg
+
+
+def famudra_decode_bytes(cfg, pos, wbytes=2):
+    """Algorithmic HBM bytes of one decoded token at position pos: every matrix the token touches once (top-k experts only), the
+    fp32 latent rows of the attention layers, the head."""
+    E_ = cfg["width"]; b = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "rglru":
+            C = m["width"]; b += wbytes * (2 * C * E_ + 2 * C * (C // m["blocks"]) + E_ * C)
+        else:
+            H, D, VD, R, QR = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            b += wbytes * ((QR + R) * E_ + H * D * QR + H * D * R + H * VD * R + E_ * H * VD) + 4.0 * R * (pos + 1)
+        f = L.get("mlp")
+        if f:
+            b += 4.0 * f["router"]["experts"] * E_ + wbytes * 2 * E_ * (f["router"]["top"] * f["expert"]["ff"] + (f["shared"]["ff"] if f.get("shared") else 0))
+    return b + wbytes * cfg["vocab"] * E_
+
+
+def famudra_flops_per_token(cfg, ctx):
+    """2 x multiply-adds per token of a prefill portion whose mean context is ctx keys (head left out: a portion asks for no logits)."""
+    return 2.0 * (famudra_decode_bytes(cfg, 0, 1) - cfg["vocab"] * cfg["width"]) + sum(
+        4.0 * L["mixer"]["heads"] * L["mixer"]["kv_rank"] * ctx for L in cfg["layers"] if L["type"] == "latent_attention")
+
+
+def famudra_bench(args):
+    from nano_b200 import engine as E
+    hbm, hbm_src = peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    ctx, n_dec, T = 1024, 128, 2048
+    sampler = ClockSampler(0); sampler.start()
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else sorted(FAMUDRA_SIZES)):
+        path, cfg = famudra_model(name)
+        rng = np.random.default_rng(0)
+        row = {}
+        for mode, flags in (("bf16", 0), ("f32", E.FLAG_F32)):
+            if mode == "f32" and not args.with_f32:
+                continue
+            eng = E.Engine(path, ctx + n_dec + T + 64, flags=flags)
+            ids = np.zeros(ctx + n_dec + 8, np.uint32); ids[:ctx] = rng.integers(0, FAMUDRA_VOCAB, ctx)
+            for _ in range(max(1, min(args.warmup, 3))):
+                eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
+            l0 = eng.launches
+            pre_ms, dec_ms = eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
+            launches = eng.launches - l0
+            s = eng.seq_open()
+            pf_ms = eng.step_timed(s, rng.integers(0, FAMUDRA_VOCAB, T).astype(np.uint32), max(1, args.steps))
+            eng.seq_close(s)
+            wb = 2 if mode == "bf16" else 4
+            bts = famudra_decode_bytes(cfg, ctx + n_dec / 2, wb)
+            fl = famudra_flops_per_token(cfg, T / 2)
+            row[mode] = {"decode_tok_s": n_dec / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / n_dec, "decode_bytes_per_token": bts,
+                         "decode_hbm_frac": bts * n_dec / (dec_ms * 1e-3) / (hbm * 1e9), "launches_per_token": eng.launches_per_token,
+                         "prefill_tok_s": T / (pf_ms * 1e-3), "prefill_portion": T, "prefill_tflops": fl * T / (pf_ms * 1e-3) / 1e12,
+                         "prefill_frac_of_bf16_peak": fl * T / (pf_ms * 1e-3) / 1e12 / tf if mode == "bf16" else None,
+                         "prompt_1024_ms": pre_ms, "gpu_launches": int(launches), "weight_bytes": eng.weight_bytes}
+            eng.close()
+        # the closest model of the engine: Qwen3 architecture, same width and depth, Q80 model file; its prompt runs position by position
+        E_, L = FAMUDRA_SIZES[name][0], FAMUDRA_SIZES[name][1]
+        spec = mf.ModelSpec(f"peer-{name}", mf.ARCH_QWEN3, ctx + n_dec + 8, FAMUDRA_VOCAB, L, E_, 16, 8, FAMUDRA_SIZES[name][-1], 128)
+        peer = E.Engine(mf.cached_model(spec, mf.QUANT_Q80, 128, fast=True), ctx + n_dec + 8)
+        pid = np.zeros(ctx + n_dec + 8, np.uint32); pid[:ctx] = rng.integers(0, FAMUDRA_VOCAB, ctx)
+        peer.decode_greedy(pid.copy(), ctx, ctx + n_dec)
+        ppre, pdec = peer.decode_greedy(pid.copy(), ctx, ctx + n_dec)
+        pb = spec.bytes_per_token(mf.QUANT_Q80, 128, ctx + n_dec / 2)
+        row["peer_qwen3_q80"] = {"decode_tok_s": n_dec / (pdec * 1e-3), "decode_bytes_per_token": pb, "decode_hbm_frac": pb * n_dec / (pdec * 1e-3) / (hbm * 1e9),
+                                 "prefill_tok_s": (ctx - 1) / (ppre * 1e-3), "engine": peer.path, "weight_bytes": peer.weight_bytes}
+        peer.close()
+        out[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "famudra", "unit": "tokens/s", "n_gpus": 1, "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf},
+                      "config": {"decode": f"greedy device loop, {n_dec} tokens after a {ctx}-token prompt, batch 1", "prefill": f"one portion of {T} tokens into an empty sequence",
+                                 "timing": "CUDA events on the engine's stream after warm-up", "l2": "weights of one token exceed the 126 MB L2 at w2048; at w1024 the active weights fit and the fraction is against HBM all the same"},
+                      "clocks": clocks, "sizes": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -495,7 +601,13 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-stream", action="store_true", help="forbid the streaming kernel")
+    ap.add_argument("--design", default=None, choices=["famudra"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
+    ap.add_argument("--sizes", default=None, help="--design: comma-separated size names (default: all)")
+    ap.add_argument("--with-f32", action="store_true", help="--design: also time the true-32-bit mode")
     args = ap.parse_args()
+    if args.design == "famudra":
+        famudra_bench(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     preset, quant, gs, seq = WORKLOADS[args.workload]

@@ -88,11 +88,13 @@ struct LayeredEngine : nb::EngineBase {
     float *x = nullptr, *x0 = nullptr, *hm = nullptr, *h2 = nullptr, *d = nullptr;
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
-    float *b_zr = nullptr, *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
+    float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
     float *b_xn = nullptr, *logits = nullptr, *keep = nullptr;
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
+    uint32_t *dpos = nullptr, *zero_dev = nullptr;            // device-side position of a captured decode step; a constant 0
+    bool use_graph = true; std::vector<cudaGraphExec_t> graphs; uint32_t graph_launches = 0;
     // generation on the implicit sequence
     int gen_seq = -1;
     void *samp_ws = nullptr; size_t samp_cub = 0; uint32_t *samp_host = nullptr;
@@ -283,17 +285,33 @@ GemmArgs plain(const float *A, uint32_t lda, const Weight &w, float *C, uint32_t
 
 uint32_t ew_grid(size_t n) { return (uint32_t)std::min<size_t>((n + 255) / 256, 148 * 16); }
 
+constexpr int kAttnQT = 4;      // query tokens per attention block in a prefill portion
+size_t attn_smem(uint32_t R, int qt) { return ((size_t)qt * kAttnWarps * R + (size_t)kPage * (R + 1)) * 4; }
+
+template <int QT>
+int attn_launch_qt(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
+    const dim3 grid((a.T + QT - 1) / QT, a.nsplit, (a.H + kAttnWarps - 1) / kAttnWarps), block(kAttnWarps * 32);
+    const size_t smem = attn_smem(a.R, QT);
+    if (rch <= 2) return launch<AttnArgs>(e, k_latent_attn<2, QT>, grid, block, smem, a);
+    if (rch <= 4) return launch<AttnArgs>(e, k_latent_attn<4, QT>, grid, block, smem, a);
+    if (rch <= 8) return launch<AttnArgs>(e, k_latent_attn<8, QT>, grid, block, smem, a);
+    return launch<AttnArgs>(e, k_latent_attn<16, QT>, grid, block, smem, a);
+}
 int attn_launch(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
-    const size_t smem = ((size_t)kAttnWarps * a.R + (size_t)kPage * (a.R + 1)) * 4;
-    const dim3 grid(a.T, a.nsplit, (a.H + kAttnWarps - 1) / kAttnWarps), block(kAttnWarps * 32);
-    if (rch <= 2) return launch<AttnArgs>(e, k_latent_attn<2>, grid, block, smem, a);
-    if (rch <= 4) return launch<AttnArgs>(e, k_latent_attn<4>, grid, block, smem, a);
-    if (rch <= 8) return launch<AttnArgs>(e, k_latent_attn<8>, grid, block, smem, a);
-    return launch<AttnArgs>(e, k_latent_attn<16>, grid, block, smem, a);
+    return a.T > kGemvMaxM ? attn_launch_qt<kAttnQT>(e, a, rch) : attn_launch_qt<1>(e, a, rch);
+}
+template <int QT>
+int attn_optin(int smem) {
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<2, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<4, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<8, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<16, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    return 0;
 }
 
 // every layer run over T tokens (x already holds their embeddings) of the sequence in `slot`, whose first token sits at pos0
-int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0) {
+// (+ *pos_ptr: a captured decode step keeps the position on the device and uses a fixed number of key splits)
+int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const uint32_t *pos_ptr = nullptr) {
     const uint32_t E = e->E;
     float *st = e->state + (size_t)slot * e->slot_floats;
     const uint32_t *table = e->table + (size_t)slot * e->n_pages;
@@ -310,29 +328,34 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0) {
             const uint32_t C = L.C, bs = C / L.blocks;
             if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
             ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
-            if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
-            if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
+            if (T <= kGemvMaxM) { if ((r = launch<ConvArgs>(e, k_conv_small, dim3((C + 127) / 128), dim3(128), 0, ca))) return r; }
+            else {
+                if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
+                if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
+            }
             GemmArgs g{};
             g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
             g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
             if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
             ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
-            if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r;
+            if (T <= 32) { if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r; }
+            else if ((r = launch<ScanArgs>(e, k_rglru_scan_par, dim3((C + 31) / 32), dim3(32, T >= 256 ? 32 : 8), 0, sa))) return r;
             if ((r = gemm(e, plain(e->b_sy, C, L.o, e->d, E, T), 1, T))) return r;
         } else {
             const uint32_t H = L.H, R = L.R, QR = L.QR;
             if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
-            LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps};
+            LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
             if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
             if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
             GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
             g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
             g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
             if ((r = gemm(e, g, H, T))) return r;
-            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale};
-            if (T <= kGemvMaxM) {
+            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr};
+            if (pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
+            else if (T <= kGemvMaxM) {
                 const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
-                aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 4u));
+                aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
             }
             if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
             if (aa.nsplit > 1 && (r = launch<AttnArgs>(e, k_attn_merge, dim3(T, H), dim3(64), 0, aa))) return r;
@@ -344,11 +367,9 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0) {
         }
         CombineArgs c{e->x, e->d, nullptr, nullptr, nullptr, nullptr, e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr, T, E, 0};
         if (L.has_mlp) {
-            Weight rw; rw.p = L.router; rw.rows = L.NE; rw.cols = E;
-            if ((r = gemm(e, plain(e->h2, E, rw, e->b_zr, L.NE, T), 1, T, true))) return r;
-            RouteArgs ra{e->b_zr, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top};
-            if ((r = launch<RouteArgs>(e, k_route, dim3((T + 63) / 64), dim3(64), 0, ra)) || (r = launch<RouteArgs>(e, k_route_scan, dim3(1), dim3(32), 0, ra)) ||
-                (r = launch<RouteArgs>(e, k_route_scatter, dim3((T * L.top + 127) / 128), dim3(128), 0, ra))) return r;
+            RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E};
+            if ((r = launch<RouteArgs>(e, k_route, dim3((T + 7) / 8), dim3(256), (size_t)8 * L.NE * 4, ra)) ||
+                (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
             GemmArgs u{};
             u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.C = e->b_hb; u.ldc = L.ff; u.M = T; u.N = L.ff; u.K = E; u.a_gmod = 1;
             u.g_off = e->b_off; u.a_rows = e->b_rows; u.w_gstride = (uint64_t)L.ff * E; u.epi = EPI_RELU2;
@@ -368,20 +389,51 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0) {
     return 0;
 }
 
-int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T) {
-    if (e->f32) k_embed<float><<<T, 128, 0, e->stream>>>(tok_dev, (const float *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
-    else k_embed<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, (const __nv_bfloat16 *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
+int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr) {
+    if (e->f32) k_embed<float><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const float *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
+    else k_embed<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const __nv_bfloat16 *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
     CK(cudaGetLastError());
     e->launches++;
     return 0;
 }
 
 // logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
-int head_rows(LayeredEngine *e, uint32_t nw) {
-    k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
+int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr) {
+    k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
     CK(cudaGetLastError());
     e->launches++;
     return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);
+}
+
+// One decode step of `slot`: the token ids_dev[*dpos] at position *dpos, logits of it in e->logits[0..V).  The position lives in
+// the device word dpos, so the launch sequence is the same for every step: it is captured once per slot into a CUDA graph and
+// replayed (NB200_FLAG_NO_GRAPH: launched directly).  The caller has reserved the page and set *dpos.
+int decode_launches(LayeredEngine *e, uint32_t slot) {
+    int r;
+    if ((r = embed_tokens(e, e->ids_dev, 1, e->dpos)) || (r = run_layers(e, slot, 1, 0, e->dpos))) return r;
+    return head_rows(e, 1, e->zero_dev);
+}
+
+int decode_step(LayeredEngine *e, uint32_t slot) {
+    if (!e->use_graph || e->keep) return decode_launches(e, slot);
+    if (!e->graphs[slot]) {
+        cudaGraph_t g = nullptr;
+        const uint64_t before = e->launches;
+        CK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        int r = decode_launches(e, slot);
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+        e->graph_launches = (uint32_t)(e->launches - before);
+        e->launches = before;
+        if (r) { if (g) cudaGraphDestroy(g); return r; }
+        if (ce != cudaSuccess) return fail(NB200_ECUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+        ce = cudaGraphInstantiate(&e->graphs[slot], g, 0);
+        cudaGraphDestroy(g);
+        if (ce != cudaSuccess) { e->graphs[slot] = nullptr; return fail(NB200_ECUDA, "graph instantiate failed: %s", cudaGetErrorString(ce)); }
+    }
+    CK(cudaGraphLaunch(e->graphs[slot], e->stream));
+    e->launches += e->graph_launches;
+    e->last_T = 1;
+    return 0;
 }
 
 // ---------------- state manager ----------------
@@ -463,6 +515,17 @@ int lm_step(nb200_engine *h, uint32_t seq, const uint32_t *tokens, uint32_t n, c
     if ((r = seq_check(e, seq)) || (r = check_tokens(e, tokens, n))) return r;
     for (uint32_t i = 0; i < n_want; i++) if (want[i] >= n || (i && want[i] <= want[i - 1])) return fail(NB200_EINVAL, "want[] must be ascending indices into this step's tokens");
     CK(cudaSetDevice(e->device));
+    if (n == 1) {          // a single token: the captured decode step
+        Seq &s = e->seqs[seq];
+        if ((r = reserve_pages(e, seq, s.len + 1))) return r;
+        CK(cudaMemcpyAsync(e->ids_dev + s.len, tokens, 4, cudaMemcpyHostToDevice, e->stream));
+        CK(cudaMemcpyAsync(e->dpos, &s.len, 4, cudaMemcpyHostToDevice, e->stream));
+        if ((r = decode_step(e, seq))) return r;
+        s.len += 1;
+        if (n_want) CK(cudaMemcpyAsync(logits, e->logits, (size_t)e->V * 4, cudaMemcpyDeviceToHost, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        return 0;
+    }
     std::vector<uint32_t> done;
     for (uint32_t c0 = 0; c0 < n; c0 += e->max_tokens) {          // the staging buffer holds max_tokens ids
         const uint32_t m = std::min(e->max_tokens, n - c0);
@@ -551,14 +614,14 @@ int gen_seek(LayeredEngine *e, const uint32_t *ids, uint32_t pos) {
 int gen_token(LayeredEngine *e, uint32_t token) {
     int r;
     if (token >= e->V) return fail(NB200_EINVAL, "token/pos out of range");
-    const uint32_t zero = 0;
-    CK(cudaMemcpyAsync(e->ids_dev, &token, 4, cudaMemcpyHostToDevice, e->stream));
-    CK(cudaMemcpyAsync(e->want_dev, &zero, 4, cudaMemcpyHostToDevice, e->stream));
-    CK(cudaStreamSynchronize(e->stream));
     const uint32_t seq = (uint32_t)e->gen_seq;
-    if ((r = reserve_pages(e, seq, e->seqs[seq].len + 1)) || (r = embed_tokens(e, e->ids_dev, 1)) || (r = run_layers(e, seq, 1, e->seqs[seq].len))) return r;
-    e->seqs[seq].len += 1;
-    return head_rows(e, 1);
+    Seq &s = e->seqs[seq];
+    if ((r = reserve_pages(e, seq, s.len + 1))) return r;
+    CK(cudaMemcpyAsync(e->ids_dev + s.len, &token, 4, cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemcpyAsync(e->dpos, &s.len, 4, cudaMemcpyHostToDevice, e->stream));
+    if ((r = decode_step(e, seq))) return r;
+    s.len += 1;
+    return 0;
 }
 
 int lm_forward(nb200_engine *h, uint32_t token, uint32_t pos, uint32_t is_causal) {
@@ -602,7 +665,7 @@ int lm_next_greedy(nb200_engine *h, const uint32_t *ids, uint32_t pos, int is_pr
     if ((r = gen_seek(e, ids, pos)) || (r = gen_token(e, ids[pos]))) return r;
     const float pen = is_prefilling ? 1.0f : penalty;
     if (pen != 1.0f && (r = mark_seen(e, ids, pos))) return r;
-    PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, pen, 0};
+    PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, pen, 0, nullptr};
     if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
     CK(cudaMemcpyAsync(e->tok_host, e->next_dev, 4, cudaMemcpyDeviceToHost, e->stream));
     CK(cudaStreamSynchronize(e->stream));
@@ -624,7 +687,7 @@ int lm_next_sampled(nb200_engine *h, const uint32_t *ids, uint32_t pos, float pe
     if ((r = gen_seek(e, ids, pos)) || (r = gen_token(e, ids[pos]))) return r;
     if (penalty != 1.0f) {      // k_pick applies the penalty to the logits in place; its greedy choice is not used
         if ((r = mark_seen(e, ids, pos))) return r;
-        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, penalty, 0};
+        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, 0, 0, penalty, 0, nullptr};
         if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
     }
     uint32_t *out_dev = nullptr;
@@ -655,8 +718,6 @@ int lm_decode_greedy(nb200_engine *h, uint32_t *ids, uint32_t n_prompt, uint32_t
     CK(cudaMemcpyAsync(e->ids_dev, ids, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, e->stream));
     CK(cudaMemsetAsync(e->seen, 0, e->V, e->stream));
     CK(cudaStreamSynchronize(e->stream));
-    const uint32_t zero = 0;
-    CK(cudaMemcpyAsync(e->want_dev, &zero, 4, cudaMemcpyHostToDevice, e->stream));
     CK(cudaEventRecord(evs.ev[0], e->stream));
     if (n_prompt > 1) {
         if ((r = step_dev(e, seq, e->ids_dev, n_prompt - 1, nullptr, 0, nullptr))) return r;
@@ -664,10 +725,12 @@ int lm_decode_greedy(nb200_engine *h, uint32_t *ids, uint32_t n_prompt, uint32_t
     }
     CK(cudaEventRecord(evs.ev[1], e->stream));
     const uint64_t before = e->launches;
-    for (uint32_t pos = n_prompt - 1; pos + 1 < n_total; pos++) {
-        if ((r = embed_tokens(e, e->ids_dev + pos, 1)) || (r = run_layers(e, seq, 1, pos)) || (r = head_rows(e, 1))) return r;
+    const uint32_t first = n_prompt - 1;
+    CK(cudaMemcpyAsync(e->dpos, &first, 4, cudaMemcpyHostToDevice, e->stream));
+    for (uint32_t pos = first; pos + 1 < n_total; pos++) {      // the position and the chosen token move on the device (k_pick)
+        if ((r = decode_step(e, seq))) return r;
         s.len = pos + 1;
-        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, pos, n_prompt, penalty, 1};
+        PickArgs p{e->logits, e->seen, e->seen, e->ids_dev, e->next_dev, e->V, pos, n_prompt, penalty, 1, e->dpos};
         if ((r = launch<PickArgs>(e, k_pick, dim3(1), dim3(1024), 0, p))) return r;
     }
     if (n_total > n_prompt) e->launches_per_token = (uint32_t)((e->launches - before) / (n_total - n_prompt));
@@ -687,7 +750,7 @@ int lm_get_config(const nb200_engine *h, nb200_config *c) {
     memset(c, 0, sizeof *c);
     c->arch = NB200_ARCH_LAYERED; c->quant = e->f32 ? 0x00u : 0x16u;      // 0x16: bfloat16 weights as stored
     c->vocab_size = e->V; c->n_layer = (uint32_t)e->runs.size(); c->n_embd = e->E; c->max_seq_len = e->max_tokens; c->tp_size = 1;
-    c->reserved[0] = 0; c->reserved[3] = (uint32_t)e->layers.size(); c->reserved[4] = e->chunk_cap; c->reserved[5] = e->n_pages; c->reserved[6] = (uint32_t)e->free_pages.size();
+    c->reserved[0] = e->use_graph ? 1u : 0u; c->reserved[3] = (uint32_t)e->layers.size(); c->reserved[4] = e->chunk_cap; c->reserved[5] = e->n_pages; c->reserved[6] = (uint32_t)e->free_pages.size();
     return 0;
 }
 
@@ -695,6 +758,7 @@ void lm_destroy(nb200_engine *h) {
     LayeredEngine *e = self(h);
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
+    for (cudaGraphExec_t g : e->graphs) if (g) cudaGraphExecDestroy(g);
     for (void *p : e->allocs) cudaFree(p);
     if (e->tok_host) cudaFreeHost(e->tok_host);
     if (e->samp_host) cudaFreeHost(e->samp_host);
@@ -781,21 +845,19 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         uint32_t mPart = 0, mR = 0;
         for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.R); }
         DM(e->b_part, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
-        const int smem = (int)(((size_t)kAttnWarps * mR + (size_t)kPage * (mR + 1)) * 4);
-        if (smem > 48 * 1024) {
-            CK(cudaFuncSetAttribute((const void *)k_latent_attn<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            CK(cudaFuncSetAttribute((const void *)k_latent_attn<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            CK(cudaFuncSetAttribute((const void *)k_latent_attn<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            CK(cudaFuncSetAttribute((const void *)k_latent_attn<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        }
+        if (attn_smem(mR, kAttnQT) > 48 * 1024 && (r = attn_optin<kAttnQT>((int)attn_smem(mR, kAttnQT)))) return r;
+        if (attn_smem(mR, 1) > 48 * 1024 && (r = attn_optin<1>((int)attn_smem(mR, 1)))) return r;
     }
     if (mNE) {
-        DM(e->b_zr, T * mNE * 4); DM(e->b_idx, T * mTop * 4); DM(e->b_wt, T * mTop * 4); DM(e->b_slot, T * mTop * 4); DM(e->b_rows, T * mTop * 4);
+        DM(e->b_idx, T * mTop * 4); DM(e->b_wt, T * mTop * 4); DM(e->b_slot, T * mTop * 4); DM(e->b_rows, T * mTop * 4);
         DM(e->b_cnt, (size_t)mNE * 4); DM(e->b_off, ((size_t)mNE + 1) * 4); DM(e->b_fill, (size_t)mNE * 4);
         CK(cudaMemset(e->b_cnt, 0, (size_t)mNE * 4));
         DM(e->b_hb, T * mFF * 4); DM(e->b_eo, T * mTop * E * 4);
         if (mSFF) { DM(e->b_sh, T * mSFF * 4); DM(e->b_so, T * E * 4); }
     }
+    DM(e->dpos, 64); DM(e->zero_dev, 64);
+    CK(cudaMemset(e->dpos, 0, 64)); CK(cudaMemset(e->zero_dev, 0, 64));
+    e->graphs.assign(e->max_seqs, nullptr);
     DM(e->b_xn, (size_t)kWantBatch * E * 4); DM(e->logits, (size_t)kWantBatch * e->V * 4);
     DM(e->ids_dev, ((size_t)max_tokens + 16) * 4); DM(e->want_dev, kWantBatch * 4); DM(e->next_dev, 64); DM(e->seen, e->V);
     CK(cudaMemset(e->ids_dev, 0, ((size_t)max_tokens + 16) * 4));
@@ -813,6 +875,7 @@ extern "C" int nb_family_layered_create(nb200_engine **out, const nb::ModelDir *
     LayeredEngine *e = new LayeredEngine();
     e->ops = &kLayeredOps;
     e->device = device; e->f32 = (flags & NB200_FLAG_F32) != 0;
+    e->use_graph = !(flags & NB200_FLAG_NO_GRAPH) && !env_u32("NB200_NO_GRAPH", 0);
     cudaDeviceProp prop;
     cudaError_t ce = cudaGetDeviceProperties(&prop, device);
     if (ce == cudaSuccess) { e->num_sms = prop.multiProcessorCount; ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking); }

@@ -10,11 +10,12 @@
 //   norms                k_norm_shift (RMS norm with ONE scalar gain, two gains of the same x at once, + token shift of the mixer's
 //                        input against the previous token's input, carried in the sequence state), k_latent_norm (vector-gain RMS norm
 //                        of the query latent and of the key/value latent, the latter written into the paged cache), k_final_norm
-//   recurrence           k_conv / k_conv_state (causal per-channel convolution with its taps-1 tail in the state), k_rglru_scan
-//                        (real-gated linear recurrent unit: a = exp(-c r softplus(lam)), S = a S + sqrt(1 - a^2) i u, fp32 state)
+//   recurrence           k_conv / k_conv_state / k_conv_small (causal per-channel convolution with its taps-1 tail in the state),
+//                        k_rglru_scan (real-gated linear recurrent unit: a = exp(-c r softplus(lam)), S = a S + sqrt(1 - a^2) i u, fp32
+//                        state; token by token) and k_rglru_scan_par (the same, parallel over time segments, for long portions)
 //   attention            k_latent_attn (softmax attention of absorbed queries directly over cached latents: the latent is key AND
 //                        value, positions-free, causal; split over the keys for decode) + k_attn_merge
-//   mixture of experts   k_route (fp32 logits -> top-k, softmax over the chosen), k_route_scan, k_route_scatter (expert-sorted slots),
+//   mixture of experts   k_route (fp32 router logits -> top-k, softmax over the chosen), k_route_place (expert-sorted slots),
 //                        k_combine (weighted sum in choice order + shared expert + mixer output -> residual)
 //
 // What is fp32 here regardless of the weight type: the residual stream, every norm, router logits, attention scores / weights /
@@ -325,11 +326,13 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
     return s;
 }
 
-// x[t] = embed[token]; x0 keeps a copy when a later pass adds the embedding output again
+// x[t] = embed[tokens[base + t]]; x0 keeps a copy when a later pass adds the embedding output again.  base = *pos_ptr when given: a
+// captured decode step reads "the token at the sequence's present position" without a host-side argument
 template <typename WT>
-__global__ void k_embed(const uint32_t *__restrict__ tokens, const WT *__restrict__ embed, float *__restrict__ x, float *__restrict__ x0, uint32_t E) {
+__global__ void k_embed(const uint32_t *__restrict__ tokens, const uint32_t *__restrict__ pos_ptr, const WT *__restrict__ embed, float *__restrict__ x,
+                        float *__restrict__ x0, uint32_t E) {
     const uint32_t t = blockIdx.x;
-    const WT *src = embed + (size_t)tokens[t] * E;
+    const WT *src = embed + (size_t)tokens[t + (pos_ptr ? *pos_ptr : 0u)] * E;
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
         const float v = wval(src + i);
         x[(size_t)t * E + i] = v;
@@ -398,6 +401,25 @@ __global__ void k_conv_state(const ConvArgs a) {     // after k_conv: the tail b
     }
 }
 
+// both steps in one launch for short portions: one thread per channel, tokens in order, then the tail
+__global__ void k_conv_small(const ConvArgs a) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    for (uint32_t t = 0; t < a.T; t++) {
+        float s = a.bias[c];
+        for (uint32_t j = 0; j < a.K; j++) {
+            const int64_t src = (int64_t)t - (int64_t)(a.K - 1 - j);
+            const float v = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)((int64_t)(a.K - 1) + src) * a.C + c];
+            s = fmaf(a.taps[(size_t)c * a.K + j], v, s);
+        }
+        a.u[(size_t)t * a.C + c] = s;
+    }
+    for (uint32_t j = 0; j + 1 < a.K; j++) {
+        const int64_t src = (int64_t)a.T - (int64_t)(a.K - 1) + j;
+        a.state[(size_t)j * a.C + c] = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)(j + a.T) * a.C + c];
+    }
+}
+
 // real-gated linear recurrent unit, one thread per channel, tokens in order:
 //   a = exp(-c_decay * r * softplus(lam)),  S <- a S + sqrt(1 - a^2) * (i * u),  out = S * y
 struct ScanArgs { const float *gates; uint32_t ldg; const float *u; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C; float c_decay; };
@@ -416,9 +438,44 @@ __global__ void k_rglru_scan(const ScanArgs a) {
     a.S[c] = S;
 }
 
+// The same recurrence for long portions, parallel over time: the portion is cut into blockDim.y segments.  A thread (channel,
+// segment) first composes its segment's affine map S -> P S + Q, the segment-0 threads chain the maps to every segment's entry
+// state (and the portion's final state), then each thread replays its segment from its entry state and writes the outputs.
+__global__ void __launch_bounds__(1024) k_rglru_scan_par(const ScanArgs a) {
+    __shared__ float P[32][33], Q[32][33];
+    const uint32_t x = threadIdx.x, seg = threadIdx.y, nseg = blockDim.y, c = blockIdx.x * 32u + x;
+    const uint32_t Ls = (a.T + nseg - 1u) / nseg, t0 = min(a.T, seg * Ls), t1 = min(a.T, t0 + Ls);
+    const bool live = c < a.C;
+    const float sp = live ? softplusf_(a.lam[c]) : 0.0f;
+    float p = 1.0f, q = 0.0f;
+    if (live)
+        for (uint32_t t = t0; t < t1; t++) {
+            const float r = a.gates[(size_t)t * a.ldg + c], i = a.gates[(size_t)t * a.ldg + a.C + c];
+            const float av = expf(-a.c_decay * r * sp);
+            q = av * q + sqrtf(1.0f - av * av) * (i * a.u[(size_t)t * a.C + c]);
+            p *= av;
+        }
+    P[seg][x] = p; Q[seg][x] = q;
+    __syncthreads();
+    if (seg == 0 && live) {
+        float s = a.S[c];
+        for (uint32_t g = 0; g < nseg; g++) { const float pg = P[g][x], qg = Q[g][x]; P[g][x] = s; s = pg * s + qg; }
+        a.S[c] = s;
+    }
+    __syncthreads();
+    if (!live) return;
+    float S = P[seg][x];
+    for (uint32_t t = t0; t < t1; t++) {
+        const float r = a.gates[(size_t)t * a.ldg + c], i = a.gates[(size_t)t * a.ldg + a.C + c];
+        const float av = expf(-a.c_decay * r * sp);
+        S = av * S + sqrtf(1.0f - av * av) * (i * a.u[(size_t)t * a.C + c]);
+        a.out[(size_t)t * a.C + c] = S * a.y[(size_t)t * a.ldy + c];
+    }
+}
+
 // vector-gain RMS norms of the two latents of one token: z = [query latent | key/value latent]; the query latent goes to cq, the
 // key/value latent into the sequence's cache page of position pos0 + t
-struct LatentNormArgs { const float *z; uint32_t ldz; const float *wq, *wkv; float *cq; float *cache; const uint32_t *table; uint32_t QR, R, pos0; float eps; };
+struct LatentNormArgs { const float *z; uint32_t ldz; const float *wq, *wkv; float *cq; float *cache; const uint32_t *table; uint32_t QR, R, pos0; float eps; const uint32_t *pos_ptr; };
 __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
     __shared__ float red[32];
     const uint32_t t = blockIdx.x;
@@ -430,84 +487,119 @@ __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
     s2 = block_sum(s2, red);
     const float rq = 1.0f / sqrtf(s / (float)a.QR + a.eps), rk = 1.0f / sqrtf(s2 / (float)a.R + a.eps);
     for (uint32_t i = threadIdx.x; i < a.QR; i += blockDim.x) a.cq[(size_t)t * a.QR + i] = z[i] * rq * a.wq[i];
-    const uint32_t pos = a.pos0 + t;
+    const uint32_t pos = a.pos0 + t + (a.pos_ptr ? *a.pos_ptr : 0u);
     float *row = a.cache + ((size_t)a.table[pos / kPage] * kPage + pos % kPage) * a.R;
     for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) row[i] = z[a.QR + i] * rk * a.wkv[i];
 }
 
 // Softmax attention over cached latents.  qa[t][h][:] is head h's query already multiplied into latent space (q_h^T W_uk,h), so
 // score(t, j) = scale * qa[t][h] . c_j and the head's output in latent space is sum_j p_j c_j (multiplied by W_uv,h afterwards):
-// the latent row is key and value at once and is read once for all heads of a block.  Causal: keys 0 .. pos0 + t.
-// grid = (tokens, key splits, head groups of kAttnWarps); one warp per head; lanes = keys for the scores, = latent columns for the
-// weighted sum; online softmax in fp32.  With one split the normalised result is written; otherwise partial (o, m, l) triples.
+// the latent row is key and value at once and a block reads it once for QT query tokens x kAttnWarps heads.  Causal: query t sees
+// keys 0 .. pos + t, pos = pos0 (+ *pos_ptr in a captured decode step).
+// grid = (query tiles of QT tokens, key splits, head groups); one warp per head; lanes = keys for the scores, = latent columns for
+// the weighted sum; online softmax in fp32.  A key tile (one cache page) is fetched with all of a thread's 16-byte loads in flight
+// at once.  With one split the normalised result is written; otherwise partial (o, m, l) triples for k_attn_merge.
 struct AttnArgs {
     const float *qa; const float *cache; const uint32_t *table; float *out; float *part;
-    uint32_t T, H, R, pos0, nsplit; float scale;
+    uint32_t T, H, R, pos0, nsplit; float scale; const uint32_t *pos_ptr;
 };
-template <int RCH>
+template <int RCH, int QT>
 __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
     extern __shared__ float sm[];
-    const uint32_t t = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
+    const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
+    const uint32_t nq = min((uint32_t)QT, a.T - tq0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = h0 + warp;
     const uint32_t R = a.R, LDC = R + 1u;
-    float *q_s = sm;                         // [kAttnWarps][R]
-    float *c_s = sm + kAttnWarps * R;        // [kPage][R + 1]
-    const uint32_t nkeys = a.pos0 + t + 1u, tiles = (nkeys + kPage - 1u) / kPage;
+    float *q_s = sm;                              // [QT][kAttnWarps][R]
+    float *c_s = sm + QT * kAttnWarps * R;        // [kPage][R + 1]
+    const uint32_t pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
+    const uint32_t nkeys = pos + tq0 + nq, tiles = (nkeys + kPage - 1u) / kPage;      // keys of the block's last query
     const uint32_t tps = (tiles + a.nsplit - 1u) / a.nsplit;
     const uint32_t tile_lo = split * tps, tile_hi = min(tiles, tile_lo + tps);
-    for (uint32_t i = threadIdx.x; i < kAttnWarps * R; i += blockDim.x) {
-        const uint32_t hh = h0 + i / R;
-        q_s[i] = hh < a.H ? a.qa[((size_t)t * a.H + hh) * R + i % R] : 0.0f;
+    for (uint32_t i = threadIdx.x; i < QT * kAttnWarps * R; i += blockDim.x) {
+        const uint32_t qi = i / (kAttnWarps * R), rem = i % (kAttnWarps * R), hh = h0 + rem / R;
+        q_s[i] = (qi < nq && hh < a.H) ? a.qa[((size_t)(tq0 + qi) * a.H + hh) * R + rem % R] : 0.0f;
     }
-    float m = -INFINITY, l = 0.0f, o[RCH];
+    float m[QT], l[QT], o[QT][RCH];
 #pragma unroll
-    for (int c = 0; c < RCH; c++) o[c] = 0.0f;
-    const float *qh = q_s + warp * R;
+    for (int qi = 0; qi < QT; qi++) {
+        m[qi] = -INFINITY; l[qi] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < RCH; c++) o[qi][c] = 0.0f;
+    }
+    const bool vec = (R % 4u) == 0;
     for (uint32_t tile = tile_lo; tile < tile_hi; tile++) {
         __syncthreads();
         const float *src = a.cache + (size_t)a.table[tile] * kPage * R;
         const uint32_t nk = min(kPage, nkeys - tile * kPage);
-        for (uint32_t i = threadIdx.x; i < nk * R; i += blockDim.x) c_s[(i / R) * LDC + i % R] = src[i];
+        if (vec) {
+            const uint32_t n4 = nk * R / 4u;
+            const float4 *src4 = reinterpret_cast<const float4 *>(src);
+            for (uint32_t base = 0; base < n4; base += 8u * kAttnWarps * 32u) {
+                float4 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) { const uint32_t i = base + k * kAttnWarps * 32u + threadIdx.x; if (i < n4) v[k] = __ldg(src4 + i); }
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint32_t i = base + k * kAttnWarps * 32u + threadIdx.x;
+                    if (i < n4) { float *d = c_s + (i * 4u / R) * LDC + (i * 4u) % R; d[0] = v[k].x; d[1] = v[k].y; d[2] = v[k].z; d[3] = v[k].w; }
+                }
+            }
+        } else {
+            for (uint32_t i = threadIdx.x; i < nk * R; i += blockDim.x) c_s[(i / R) * LDC + i % R] = src[i];
+        }
         __syncthreads();
         if (h < a.H) {
-            float s = -INFINITY;
-            if (lane < nk) {
-                const float *cr = c_s + lane * LDC;
-                float d = 0.0f;
-                for (uint32_t r = 0; r < R; r++) d = fmaf(qh[r], cr[r], d);
-                s = d * a.scale;
-            }
-            float tm = s;
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
-            const float mn = fmaxf(m, tm);
-            const float corr = expf(m - mn);
-            const float p = lane < nk ? expf(s - mn) : 0.0f;
-            float ps = p;
+            for (int qi = 0; qi < QT; qi++) {
+                const uint32_t kq = pos + tq0 + qi + 1u;                      // keys this query sees
+                if ((uint32_t)qi >= nq || kq <= tile * kPage) continue;
+                const uint32_t nkq = min(nk, kq - tile * kPage);
+                const float *qh = q_s + ((size_t)qi * kAttnWarps + warp) * R;
+                float s = -INFINITY;
+                if (lane < nkq) {
+                    const float *cr = c_s + lane * LDC;
+                    float d = 0.0f;
+                    for (uint32_t r = 0; r < R; r++) d = fmaf(qh[r], cr[r], d);
+                    s = d * a.scale;
+                }
+                float tm = s;
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
-            l = l * corr + ps;
-            m = mn;
+                for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
+                const float mn = fmaxf(m[qi], tm);
+                const float corr = expf(m[qi] - mn);
+                const float p = lane < nkq ? expf(s - mn) : 0.0f;
+                float ps = p;
 #pragma unroll
-            for (int c = 0; c < RCH; c++) o[c] *= corr;
-            for (uint32_t j = 0; j < nk; j++) {
-                const float pj = __shfl_sync(0xffffffffu, p, j);
-                const float *cr = c_s + j * LDC;
+                for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+                l[qi] = l[qi] * corr + ps;
+                m[qi] = mn;
 #pragma unroll
-                for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) o[c] = fmaf(pj, cr[r], o[c]); }
+                for (int c = 0; c < RCH; c++) o[qi][c] *= corr;
+                for (uint32_t j = 0; j < nkq; j++) {
+                    const float pj = __shfl_sync(0xffffffffu, p, j);
+                    const float *cr = c_s + j * LDC;
+#pragma unroll
+                    for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) o[qi][c] = fmaf(pj, cr[r], o[qi][c]); }
+                }
             }
         }
     }
     if (h >= a.H) return;
-    if (a.nsplit == 1) {
-        const float inv = 1.0f / l;
 #pragma unroll
-        for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) a.out[((size_t)t * a.H + h) * R + r] = o[c] * inv; }
-    } else {
-        float *dst = a.part + (((size_t)t * a.nsplit + split) * a.H + h) * (R + 2u);
+    for (int qi = 0; qi < QT; qi++) {
+        if ((uint32_t)qi >= nq) continue;
+        const uint32_t t = tq0 + qi;
+        if (a.nsplit == 1) {
+            const float inv = 1.0f / l[qi];
 #pragma unroll
-        for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) dst[r] = o[c]; }
-        if (lane == 0) { dst[R] = m; dst[R + 1] = l; }
+            for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) a.out[((size_t)t * a.H + h) * R + r] = o[qi][c] * inv; }
+        } else {
+            float *dst = a.part + (((size_t)t * a.nsplit + split) * a.H + h) * (R + 2u);
+#pragma unroll
+            for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) dst[r] = o[qi][c]; }
+            if (lane == 0) { dst[R] = m[qi]; dst[R + 1] = l[qi]; }
+        }
     }
 }
 // grid = (tokens, heads): out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys
@@ -529,13 +621,26 @@ __global__ void k_attn_merge(const AttnArgs a) {
 // ------------------------------------------------------------------------------------------------
 // mixture of experts: routing
 // ------------------------------------------------------------------------------------------------
-// one thread per token: the `top` largest logits (ties: the lower expert index first), weights = softmax over the chosen logits;
-// counts[e] += 1 per choice
-struct RouteArgs { const float *z; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top; };
-__global__ void k_route(const RouteArgs a) {
-    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per token: router logits z_e = W_router[e] . h in fp32 (lanes stride over the width), then the `top` largest (ties: the
+// lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per choice.
+// Dynamic shared memory: warps x NE floats.
+struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E; };
+__global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
+    extern __shared__ float zs[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= a.T) return;
-    const float *z = a.z + (size_t)t * a.NE;
+    float *z = zs + warp * a.NE;
+    const float *h = a.h + (size_t)t * a.E;
+    for (uint32_t e = 0; e < a.NE; e++) {
+        const float *w = a.router + (size_t)e * a.E;
+        float acc = 0.0f;
+        for (uint32_t k = lane; k < a.E; k += 32u) acc = fmaf(h[k], w[k], acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncwarp();
+    if (lane) return;
     uint32_t *idx = a.idx + (size_t)t * a.top; float *wt = a.wt + (size_t)t * a.top;
     for (uint32_t j = 0; j < a.top; j++) {
         float best = -INFINITY; uint32_t bi = 0xffffffffu;
@@ -552,20 +657,20 @@ __global__ void k_route(const RouteArgs a) {
     for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - mx); s += wt[j]; }
     for (uint32_t j = 0; j < a.top; j++) { wt[j] /= s; atomicAdd(a.counts + idx[j], 1u); }
 }
-// one thread: off[e] = rows before expert e (off[NE] = total); clears the fill counters and the counts for the next use
-__global__ void k_route_scan(const RouteArgs a) {
-    if (threadIdx.x || blockIdx.x) return;
-    uint32_t s = 0;
-    for (uint32_t e = 0; e < a.NE; e++) { a.off[e] = s; s += a.counts[e]; a.counts[e] = 0; a.fill[e] = 0; }
-    a.off[a.NE] = s;
-}
-// slot[t][j] = row of (token t, choice j) in the expert-sorted order; rows[slot] = t
-__global__ void k_route_scatter(const RouteArgs a) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= a.T * a.top) return;
-    const uint32_t e = a.idx[i];
-    const uint32_t s = a.off[e] + atomicAdd(a.fill + e, 1u);
-    a.slot[i] = s; a.rows[s] = i / a.top;
+// One block: off[e] = rows before expert e (off[NE] = total), counters cleared for the next use; then slot[t][j] = the row of
+// (token t, choice j) in the expert-sorted order and rows[slot] = t
+__global__ void __launch_bounds__(1024) k_route_place(const RouteArgs a) {
+    if (threadIdx.x == 0) {
+        uint32_t s = 0;
+        for (uint32_t e = 0; e < a.NE; e++) { a.off[e] = s; s += a.counts[e]; a.counts[e] = 0; a.fill[e] = 0; }
+        a.off[a.NE] = s;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < a.T * a.top; i += blockDim.x) {
+        const uint32_t e = a.idx[i];
+        const uint32_t s = a.off[e] + atomicAdd(a.fill + e, 1u);
+        a.slot[i] = s; a.rows[s] = i / a.top;
+    }
 }
 
 // x[t] += d[t] + ( sum_j wt[t][j] * eo[slot[t][j]]  (+ shared[t]) ),  the sum in the order of the choices; keep (optional) gets x
@@ -602,8 +707,8 @@ __global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x,
 
 // greedy choice with the repetition penalty of the generation hosts: logits of ids seen before are divided (positive) or multiplied
 // (negative) by `penalty`; the lowest index wins ties.  One block.  ids[pos + 1] receives the choice unless that place is still
-// inside the prompt (pos + 1 < n_prompt).  penalised (optional) receives the logits after the penalty, for the sampler.
-struct PickArgs { float *logits; const uint8_t *seen; uint8_t *seen_rw; uint32_t *ids; uint32_t *next; uint32_t V, pos, n_prompt; float penalty; uint32_t advance; };
+// inside the prompt (pos + 1 < n_prompt); pos is read from (and advanced in) *pos_ptr when given.  penalised (optional) receives the logits after the penalty, for the sampler.
+struct PickArgs { float *logits; const uint8_t *seen; uint8_t *seen_rw; uint32_t *ids; uint32_t *next; uint32_t V, pos, n_prompt; float penalty; uint32_t advance; uint32_t *pos_ptr; };
 __global__ void __launch_bounds__(1024) k_pick(const PickArgs a) {
     __shared__ float bv[32]; __shared__ uint32_t bi[32];
     float best = -INFINITY; uint32_t idx = 0xffffffffu;
@@ -623,9 +728,11 @@ __global__ void __launch_bounds__(1024) k_pick(const PickArgs a) {
         for (uint32_t w = 1; w < (blockDim.x >> 5); w++)
             if (bi[w] != 0xffffffffu && (bi[0] == 0xffffffffu || bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0]))) { bv[0] = bv[w]; bi[0] = bi[w]; }
         uint32_t nxt = bi[0];
-        if (a.advance) {
-            a.seen_rw[a.ids[a.pos]] = 1;
-            if (a.pos + 1 < a.n_prompt) nxt = a.ids[a.pos + 1]; else a.ids[a.pos + 1] = nxt;
+        if (a.advance) {      // the device loop: pos lives on the device and moves on with the choice
+            const uint32_t pos = a.pos_ptr ? *a.pos_ptr : a.pos;
+            a.seen_rw[a.ids[pos]] = 1;
+            if (pos + 1 < a.n_prompt) nxt = a.ids[pos + 1]; else a.ids[pos + 1] = nxt;
+            if (a.pos_ptr) *a.pos_ptr = pos + 1;
         }
         *a.next = nxt;
     }
