@@ -74,7 +74,8 @@ constexpr uint32_t kSplitMax = 32;
 
 struct LayeredEngine : nb::EngineBase {
     int device = 0, num_sms = 148;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr, side = nullptr, cur = nullptr;      // cur: where launch() puts kernels (stream, or side for a layer's feed-forward branch)
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool f32 = false;
     uint32_t V = 0, E = 0; float eps = 0.0f;
     std::vector<Layer> layers; std::vector<Run> runs;
@@ -255,7 +256,7 @@ int load_moe(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint
 // ---------------- launches ----------------
 template <typename A>
 int launch(LayeredEngine *e, void (*k)(const A), dim3 grid, dim3 block, size_t smem, const A &args) {
-    k<<<grid, block, smem, e->stream>>>(args);
+    k<<<grid, block, smem, e->cur>>>(args);
     CK(cudaGetLastError());
     e->launches++;
     return 0;
@@ -285,8 +286,8 @@ GemmArgs plain(const float *A, uint32_t lda, const Weight &w, float *C, uint32_t
 
 uint32_t ew_grid(size_t n) { return (uint32_t)std::min<size_t>((n + 255) / 256, 148 * 16); }
 
-constexpr int kAttnQT = 4;      // query tokens per attention block in a prefill portion
-size_t attn_smem(uint32_t R, int qt) { return ((size_t)qt * kAttnWarps * R + (size_t)kPage * (R + 1)) * 4; }
+constexpr int kAttnQT = 8;      // query tokens per attention block in a prefill portion (4 where the latent is wider than 256)
+size_t attn_smem(uint32_t R, int qt) { return ((size_t)qt * kAttnWarps * R + (size_t)kPage * (R + 4)) * 4; }
 
 template <int QT>
 int attn_launch_qt(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
@@ -298,7 +299,8 @@ int attn_launch_qt(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
     return launch<AttnArgs>(e, k_latent_attn<16, QT>, grid, block, smem, a);
 }
 int attn_launch(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
-    return a.T > kGemvMaxM ? attn_launch_qt<kAttnQT>(e, a, rch) : attn_launch_qt<1>(e, a, rch);
+    if (a.T <= kGemvMaxM) return attn_launch_qt<1>(e, a, rch);
+    return rch <= 8 ? attn_launch_qt<kAttnQT>(e, a, rch) : attn_launch_qt<4>(e, a, rch);
 }
 template <int QT>
 int attn_optin(int smem) {
@@ -316,6 +318,7 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
     float *st = e->state + (size_t)slot * e->slot_floats;
     const uint32_t *table = e->table + (size_t)slot * e->n_pages;
     int r;
+    e->cur = e->stream;
     for (size_t ri = 0; ri < e->runs.size(); ri++) {
         const Run &run = e->runs[ri];
         const Layer &L = e->layers[run.layer];
@@ -323,6 +326,7 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         {
             NormShiftArgs a{e->x, L.norm1, L.has_mlp ? L.norm2 : nullptr, L.shift, st + run.st_prev, e->hm, L.has_mlp ? e->h2 : nullptr, T, E, e->eps};
             if ((r = launch<NormShiftArgs>(e, k_norm_shift, dim3(T > 1 ? T - 1 : 1), dim3(256), 0, a))) return r;
+            if (L.has_mlp) CK(cudaEventRecord(e->ev_fork, e->stream));
         }
         if (L.type == MIX_RGLRU) {
             const uint32_t C = L.C, bs = C / L.blocks;
@@ -358,7 +362,7 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
                 aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
             }
             if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
-            if (aa.nsplit > 1 && (r = launch<AttnArgs>(e, k_attn_merge, dim3(T, H), dim3(64), 0, aa))) return r;
+            if (aa.nsplit > 1 && (r = launch<AttnArgs>(e, k_attn_merge, dim3(T, H), dim3(128), 0, aa))) return r;
             GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
             v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
             v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
@@ -367,8 +371,12 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         }
         CombineArgs c{e->x, e->d, nullptr, nullptr, nullptr, nullptr, e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr, T, E, 0};
         if (L.has_mlp) {
+            // The layer is parallel: the feed-forward reads h2 = norm2(x) of the SAME x and shares no buffer with the mixer, so its
+            // kernels go to a second stream (a parallel branch of the captured decode graph) and join before the residual update.
+            e->cur = e->side;
+            CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0));
             RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E};
-            if ((r = launch<RouteArgs>(e, k_route, dim3((T + 7) / 8), dim3(256), (size_t)8 * L.NE * 4, ra)) ||
+            if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), (size_t)L.NE * 4, ra)) ||
                 (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
             GemmArgs u{};
             u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.C = e->b_hb; u.ldc = L.ff; u.M = T; u.N = L.ff; u.K = E; u.a_gmod = 1;
@@ -382,6 +390,9 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
                 if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, L.sff, T, nullptr, EPI_RELU2), 1, T)) || (r = gemm(e, plain(e->b_sh, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
             }
             c.eo = e->b_eo; c.slot = e->b_slot; c.wt = e->b_wt; c.shared = L.has_shared ? e->b_so : nullptr; c.top = L.top;
+            e->cur = e->stream;
+            CK(cudaEventRecord(e->ev_join, e->side));
+            CK(cudaStreamWaitEvent(e->stream, e->ev_join, 0));
         }
         if ((r = launch<CombineArgs>(e, k_combine, dim3(ew_grid((size_t)T * E)), dim3(256), 0, c))) return r;
     }
@@ -762,6 +773,9 @@ void lm_destroy(nb200_engine *h) {
     for (void *p : e->allocs) cudaFree(p);
     if (e->tok_host) cudaFreeHost(e->tok_host);
     if (e->samp_host) cudaFreeHost(e->samp_host);
+    if (e->ev_fork) cudaEventDestroy(e->ev_fork);
+    if (e->ev_join) cudaEventDestroy(e->ev_join);
+    if (e->side) cudaStreamDestroy(e->side);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -846,6 +860,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.R); }
         DM(e->b_part, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
         if (attn_smem(mR, kAttnQT) > 48 * 1024 && (r = attn_optin<kAttnQT>((int)attn_smem(mR, kAttnQT)))) return r;
+        if (attn_smem(mR, 4) > 48 * 1024 && (r = attn_optin<4>((int)attn_smem(mR, 4)))) return r;
         if (attn_smem(mR, 1) > 48 * 1024 && (r = attn_optin<1>((int)attn_smem(mR, 1)))) return r;
     }
     if (mNE) {
@@ -879,6 +894,10 @@ extern "C" int nb_family_layered_create(nb200_engine **out, const nb::ModelDir *
     cudaDeviceProp prop;
     cudaError_t ce = cudaGetDeviceProperties(&prop, device);
     if (ce == cudaSuccess) { e->num_sms = prop.multiProcessorCount; ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking); }
+    if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking);
+    if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming);
+    if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming);
+    e->cur = e->stream;
     int r = ce == cudaSuccess ? create(e, dir, max_tokens) : fail(NB200_ECUDA, "device setup failed: %s", cudaGetErrorString(ce));
     if (r) { lm_destroy(reinterpret_cast<nb200_engine *>(e)); return r; }
     *out = reinterpret_cast<nb200_engine *>(e);

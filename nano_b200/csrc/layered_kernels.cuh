@@ -505,13 +505,15 @@ struct AttnArgs {
 };
 template <int RCH, int QT>
 __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
     const uint32_t nq = min((uint32_t)QT, a.T - tq0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = h0 + warp;
-    const uint32_t R = a.R, LDC = R + 1u;
-    float *q_s = sm;                              // [QT][kAttnWarps][R]
-    float *c_s = sm + QT * kAttnWarps * R;        // [kPage][R + 1]
+    const uint32_t R = a.R;
+    const bool vec = (R % 4u) == 0;                // 16-byte shared-memory rows: (R + 4) / 4 is odd for R % 8 == 0, so 8 lanes hit 8 bank groups
+    const uint32_t LDC = vec ? R + 4u : R + 1u;
+    float *q_s = sm;                               // [QT][kAttnWarps][R]
+    float *c_s = sm + QT * kAttnWarps * R;         // [kPage][LDC]
     const uint32_t pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
     const uint32_t nkeys = pos + tq0 + nq, tiles = (nkeys + kPage - 1u) / kPage;      // keys of the block's last query
     const uint32_t tps = (tiles + a.nsplit - 1u) / a.nsplit;
@@ -527,7 +529,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
 #pragma unroll
         for (int c = 0; c < RCH; c++) o[qi][c] = 0.0f;
     }
-    const bool vec = (R % 4u) == 0;
     for (uint32_t tile = tile_lo; tile < tile_hi; tile++) {
         __syncthreads();
         const float *src = a.cache + (size_t)a.table[tile] * kPage * R;
@@ -542,45 +543,74 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     const uint32_t i = base + k * kAttnWarps * 32u + threadIdx.x;
-                    if (i < n4) { float *d = c_s + (i * 4u / R) * LDC + (i * 4u) % R; d[0] = v[k].x; d[1] = v[k].y; d[2] = v[k].z; d[3] = v[k].w; }
+                    if (i < n4) *reinterpret_cast<float4 *>(c_s + (i * 4u / R) * LDC + (i * 4u) % R) = v[k];
                 }
             }
         } else {
             for (uint32_t i = threadIdx.x; i < nk * R; i += blockDim.x) c_s[(i / R) * LDC + i % R] = src[i];
         }
         __syncthreads();
-        if (h < a.H) {
+        if (h >= a.H) continue;
+        uint32_t nkq[QT];               // keys of this tile each query sees (0: the tile lies after the query)
 #pragma unroll
-            for (int qi = 0; qi < QT; qi++) {
-                const uint32_t kq = pos + tq0 + qi + 1u;                      // keys this query sees
-                if ((uint32_t)qi >= nq || kq <= tile * kPage) continue;
-                const uint32_t nkq = min(nk, kq - tile * kPage);
-                const float *qh = q_s + ((size_t)qi * kAttnWarps + warp) * R;
-                float s = -INFINITY;
-                if (lane < nkq) {
-                    const float *cr = c_s + lane * LDC;
-                    float d = 0.0f;
-                    for (uint32_t r = 0; r < R; r++) d = fmaf(qh[r], cr[r], d);
-                    s = d * a.scale;
+        for (int qi = 0; qi < QT; qi++) {
+            const uint32_t kq = pos + tq0 + qi + 1u;
+            nkq[qi] = ((uint32_t)qi < nq && kq > tile * kPage) ? min(nk, kq - tile * kPage) : 0u;
+        }
+        float sc[QT];
+#pragma unroll
+        for (int qi = 0; qi < QT; qi++) sc[qi] = 0.0f;
+        const float *cr = c_s + lane * LDC;         // lanes past nk read rows of an earlier tile: their scores are masked below
+        if (vec) {
+            const float4 *c4 = reinterpret_cast<const float4 *>(cr);
+            for (uint32_t r4 = 0; r4 < R / 4u; r4++) {
+                const float4 cv = c4[r4];
+#pragma unroll
+                for (int qi = 0; qi < QT; qi++) {
+                    const float4 qv = reinterpret_cast<const float4 *>(q_s + ((size_t)qi * kAttnWarps + warp) * R)[r4];
+                    sc[qi] = fmaf(qv.w, cv.w, fmaf(qv.z, cv.z, fmaf(qv.y, cv.y, fmaf(qv.x, cv.x, sc[qi]))));
                 }
-                float tm = s;
+            }
+        } else {
+            for (uint32_t r = 0; r < R; r++) {
+                const float cv = cr[r];
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
-                const float mn = fmaxf(m[qi], tm);
-                const float corr = expf(m[qi] - mn);
-                const float p = lane < nkq ? expf(s - mn) : 0.0f;
-                float ps = p;
+                for (int qi = 0; qi < QT; qi++) sc[qi] = fmaf(q_s[((size_t)qi * kAttnWarps + warp) * R + r], cv, sc[qi]);
+            }
+        }
+        float p[QT];
+        uint32_t nkmax = 0;
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
-                l[qi] = l[qi] * corr + ps;
-                m[qi] = mn;
+        for (int qi = 0; qi < QT; qi++) {
+            const bool seen = lane < nkq[qi];
+            const float s = seen ? sc[qi] * a.scale : -INFINITY;
+            float tm = s;
 #pragma unroll
-                for (int c = 0; c < RCH; c++) o[qi][c] *= corr;
-                for (uint32_t j = 0; j < nkq; j++) {
-                    const float pj = __shfl_sync(0xffffffffu, p, j);
-                    const float *cr = c_s + j * LDC;
+            for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
+            const float mn = fmaxf(m[qi], tm);
+            const float corr = mn == -INFINITY ? 1.0f : expf(m[qi] - mn);
+            p[qi] = seen ? expf(s - mn) : 0.0f;
+            float ps = p[qi];
 #pragma unroll
-                    for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) o[qi][c] = fmaf(pj, cr[r], o[qi][c]); }
+            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+            l[qi] = l[qi] * corr + ps;
+            m[qi] = mn;
+#pragma unroll
+            for (int c = 0; c < RCH; c++) o[qi][c] *= corr;
+            nkmax = max(nkmax, nkq[qi]);
+        }
+        for (uint32_t j = 0; j < nkmax; j++) {
+            float pj[QT];
+#pragma unroll
+            for (int qi = 0; qi < QT; qi++) pj[qi] = __shfl_sync(0xffffffffu, p[qi], j);
+            const float *cj = c_s + j * LDC;
+#pragma unroll
+            for (int c = 0; c < RCH; c++) {
+                const uint32_t r = lane + 32u * c;
+                if (r < R) {
+                    const float cv = cj[r];
+#pragma unroll
+                    for (int qi = 0; qi < QT; qi++) o[qi][c] = fmaf(pj[qi], cv, o[qi][c]);
                 }
             }
         }
@@ -602,55 +632,76 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
         }
     }
 }
-// grid = (tokens, heads): out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys
-__global__ void k_attn_merge(const AttnArgs a) {
+// grid = (tokens, heads), block = 128: out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys.  The
+// (m, l) pairs of all splits are fetched at once (one per thread, nsplit <= 32), then the columns with every split's load in flight.
+__global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
+    __shared__ float w_s[32]; __shared__ float L_s;
     const uint32_t t = blockIdx.x, h = blockIdx.y, R = a.R;
     const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
     const size_t stride = (size_t)a.H * (R + 2u);
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) M = fmaxf(M, base[s * stride + R]);
-    float L = 0.0f;
-    for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) L += expf(base[s * stride + R] - M) * base[s * stride + R + 1];
+    if (threadIdx.x < 32) {
+        const uint32_t s = threadIdx.x;
+        const bool live = s < a.nsplit;
+        const float ls = live ? base[s * stride + R + 1] : 0.0f;
+        const float ms = (live && ls > 0.0f) ? base[s * stride + R] : -INFINITY;
+        float M = ms;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        const float w = ls > 0.0f ? expf(ms - M) : 0.0f;
+        float L = w * ls;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        w_s[s] = w;
+        if (s == 0) L_s = L;
+    }
+    __syncthreads();
+    const float inv = 1.0f / L_s;
     for (uint32_t r = threadIdx.x; r < R; r += blockDim.x) {
         float acc = 0.0f;
-        for (uint32_t s = 0; s < a.nsplit; s++) if (base[s * stride + R + 1] > 0.0f) acc = fmaf(expf(base[s * stride + R] - M), base[s * stride + r], acc);
-        a.out[((size_t)t * a.H + h) * R + r] = acc / L;
+#pragma unroll 8
+        for (uint32_t s = 0; s < a.nsplit; s++) acc = fmaf(w_s[s], w_s[s] > 0.0f ? base[s * stride + r] : 0.0f, acc);
+        a.out[((size_t)t * a.H + h) * R + r] = acc * inv;
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // mixture of experts: routing
 // ------------------------------------------------------------------------------------------------
-// One warp per token: router logits z_e = W_router[e] . h in fp32 (lanes stride over the width), then the `top` largest (ties: the
-// lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per choice.
-// Dynamic shared memory: warps x NE floats.
+// One block per token: router logits z_e = W_router[e] . h in fp32 (a warp per expert, lanes stride over the width), then the
+// `top` largest (ties: the lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per
+// choice.  Dynamic shared memory: NE floats.
 struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E; };
 __global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
-    extern __shared__ float zs[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= a.T) return;
-    float *z = zs + warp * a.NE;
+    extern __shared__ float z[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, t = blockIdx.x;
     const float *h = a.h + (size_t)t * a.E;
-    for (uint32_t e = 0; e < a.NE; e++) {
+    const bool vec = (a.E % 4u) == 0;
+    for (uint32_t e = warp; e < a.NE; e += blockDim.x >> 5) {
         const float *w = a.router + (size_t)e * a.E;
         float acc = 0.0f;
-        for (uint32_t k = lane; k < a.E; k += 32u) acc = fmaf(h[k], w[k], acc);
+        if (vec) {
+            for (uint32_t k = lane * 4u; k < a.E; k += 128u) {
+                const float4 hv = *reinterpret_cast<const float4 *>(h + k), wv = __ldg(reinterpret_cast<const float4 *>(w + k));
+                acc = fmaf(hv.w, wv.w, fmaf(hv.z, wv.z, fmaf(hv.y, wv.y, fmaf(hv.x, wv.x, acc))));
+            }
+        } else {
+            for (uint32_t k = lane; k < a.E; k += 32u) acc = fmaf(h[k], w[k], acc);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) z[e] = acc;
     }
-    __syncwarp();
-    if (lane) return;
+    __syncthreads();
+    if (threadIdx.x) return;
     uint32_t *idx = a.idx + (size_t)t * a.top; float *wt = a.wt + (size_t)t * a.top;
     for (uint32_t j = 0; j < a.top; j++) {
         float best = -INFINITY; uint32_t bi = 0xffffffffu;
         for (uint32_t e = 0; e < a.NE; e++) {
-            bool taken = false;
-            for (uint32_t q = 0; q < j; q++) taken = taken || idx[q] == e;
             const float v = z[e];
-            if (!taken && (bi == 0xffffffffu || v > best)) { best = v; bi = e; }
+            if (bi == 0xffffffffu || v > best) { best = v; bi = e; }
         }
         idx[j] = bi; wt[j] = best;
+        z[bi] = -INFINITY;                 // taken (a logit that IS -inf can only tie with taken ones after all finite ones are gone)
     }
     const float mx = wt[0];
     float s = 0.0f;
