@@ -74,8 +74,8 @@ constexpr uint32_t kSplitMax = 32;
 
 struct LayeredEngine : nb::EngineBase {
     int device = 0, num_sms = 148;
-    cudaStream_t stream = nullptr, side = nullptr, cur = nullptr;      // cur: where launch() puts kernels (stream, or side for a layer's feed-forward branch)
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t stream = nullptr, side = nullptr, side2 = nullptr, cur = nullptr;      // cur: where launch() puts kernels (stream, or side for a layer's feed-forward branch)
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_join2 = nullptr;
     bool f32 = false;
     uint32_t V = 0, E = 0; float eps = 0.0f;
     std::vector<Layer> layers; std::vector<Run> runs;
@@ -95,7 +95,7 @@ struct LayeredEngine : nb::EngineBase {
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
     uint32_t *dpos = nullptr, *zero_dev = nullptr;            // device-side position of a captured decode step; a constant 0
-    bool use_graph = true; std::vector<cudaGraphExec_t> graphs; uint32_t graph_launches = 0;
+    bool use_pdl = true; bool use_graph = true; std::vector<cudaGraphExec_t> graphs; uint32_t graph_launches = 0;
     // generation on the implicit sequence
     int gen_seq = -1;
     void *samp_ws = nullptr; size_t samp_cub = 0; uint32_t *samp_host = nullptr;
@@ -256,8 +256,15 @@ int load_moe(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint
 // ---------------- launches ----------------
 template <typename A>
 int launch(LayeredEngine *e, void (*k)(const A), dim3 grid, dim3 block, size_t smem, const A &args) {
-    k<<<grid, block, smem, e->cur>>>(args);
-    CK(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = e->cur;
+    cudaLaunchAttribute attr[1];
+    if (e->use_pdl) {      // programmatic dependent launch: see pdl_enter() in layered_kernels.cuh
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    CK(cudaLaunchKernelEx(&cfg, k, args));
     e->launches++;
     return 0;
 }
@@ -386,8 +393,12 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
             dn.A = e->b_hb; dn.lda = L.ff; dn.W = L.down.p; dn.ldw = L.ff; dn.C = e->b_eo; dn.ldc = E; dn.M = T; dn.N = E; dn.K = L.ff; dn.a_gmod = 1;
             dn.g_off = e->b_off; dn.w_gstride = (uint64_t)E * L.ff;
             if ((r = gemm(e, dn, L.NE, T))) return r;
-            if (L.has_shared) {
+            if (L.has_shared) {      // a third branch: the shared expert depends on h2 only
+                e->cur = e->side2;
+                CK(cudaStreamWaitEvent(e->side2, e->ev_fork, 0));
                 if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, L.sff, T, nullptr, EPI_RELU2), 1, T)) || (r = gemm(e, plain(e->b_sh, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
+                CK(cudaEventRecord(e->ev_join2, e->side2));
+                CK(cudaStreamWaitEvent(e->stream, e->ev_join2, 0));
             }
             c.eo = e->b_eo; c.slot = e->b_slot; c.wt = e->b_wt; c.shared = L.has_shared ? e->b_so : nullptr; c.top = L.top;
             e->cur = e->stream;
@@ -775,7 +786,9 @@ void lm_destroy(nb200_engine *h) {
     if (e->samp_host) cudaFreeHost(e->samp_host);
     if (e->ev_fork) cudaEventDestroy(e->ev_fork);
     if (e->ev_join) cudaEventDestroy(e->ev_join);
+    if (e->ev_join2) cudaEventDestroy(e->ev_join2);
     if (e->side) cudaStreamDestroy(e->side);
+    if (e->side2) cudaStreamDestroy(e->side2);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -890,11 +903,14 @@ extern "C" int nb_family_layered_create(nb200_engine **out, const nb::ModelDir *
     LayeredEngine *e = new LayeredEngine();
     e->ops = &kLayeredOps;
     e->device = device; e->f32 = (flags & NB200_FLAG_F32) != 0;
+    e->use_pdl = !(flags & NB200_FLAG_NO_PDL) && !env_u32("NB200_NO_PDL", 0);
     e->use_graph = !(flags & NB200_FLAG_NO_GRAPH) && !env_u32("NB200_NO_GRAPH", 0);
     cudaDeviceProp prop;
     cudaError_t ce = cudaGetDeviceProperties(&prop, device);
     if (ce == cudaSuccess) { e->num_sms = prop.multiProcessorCount; ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking); }
     if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking);
+    if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&e->side2, cudaStreamNonBlocking);
+    if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&e->ev_join2, cudaEventDisableTiming);
     if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming);
     if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming);
     e->cur = e->stream;

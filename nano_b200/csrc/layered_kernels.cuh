@@ -49,6 +49,14 @@ struct GemmArgs {
     uint32_t round_a;         // k_gemv: round A to bf16 first (what the tensor-core kernel does to its operand)
 };
 
+// Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
+// pdl_enter until this grid has finished and its writes are visible), then waits for the kernels before it.  Launch latency and block
+// scheduling of a chain of short kernels overlap with the tail of the kernel before; no kernel touches global memory before the wait.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -84,6 +92,7 @@ __device__ __forceinline__ float wval(const __nv_bfloat16 *w) { return __bfloat1
 // ------------------------------------------------------------------------------------------------
 template <typename WT>
 __global__ void __launch_bounds__(256) k_gemm_f32(const GemmArgs a) {
+    pdl_enter();
     const GroupView gv = group_view(a, blockIdx.z);
     const uint32_t m0 = blockIdx.y * 64u, n0 = blockIdx.x * 64u;
     if (m0 >= gv.rows) return;
@@ -146,6 +155,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 }
 
 __global__ void __launch_bounds__(128) k_gemm_bf16(const GemmArgs a) {
+    pdl_enter();
     const GroupView gv = group_view(a, blockIdx.z);
     const uint32_t m0 = blockIdx.y * 64u, n0 = blockIdx.x * 64u;
     if (m0 >= gv.rows) return;
@@ -257,6 +267,7 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 
 template <typename WT>
 __global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
+    pdl_enter();
     const GroupView gv = group_view(a, blockIdx.y);
     if (gv.rows == 0) return;
     const uint32_t rows = gv.rows < kGemvMaxM ? gv.rows : kGemvMaxM;
@@ -331,6 +342,7 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 template <typename WT>
 __global__ void k_embed(const uint32_t *__restrict__ tokens, const uint32_t *__restrict__ pos_ptr, const WT *__restrict__ embed, float *__restrict__ x,
                         float *__restrict__ x0, uint32_t E) {
+    pdl_enter();
     const uint32_t t = blockIdx.x;
     const WT *src = embed + (size_t)tokens[t + (pos_ptr ? *pos_ptr : 0u)] * E;
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
@@ -341,6 +353,7 @@ __global__ void k_embed(const uint32_t *__restrict__ tokens, const uint32_t *__r
 }
 
 __global__ void k_add(float *__restrict__ x, const float *__restrict__ y, size_t n) {
+    pdl_enter();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] += y[i];
 }
 
@@ -371,6 +384,7 @@ __device__ __forceinline__ void norm_shift_token(const NormShiftArgs &a, uint32_
     }
 }
 __global__ void __launch_bounds__(256) k_norm_shift(const NormShiftArgs a) {
+    pdl_enter();
     __shared__ float red[32];
     norm_shift_token(a, blockIdx.x, red);
     if (blockIdx.x == 0 && a.T > 1) { __syncthreads(); norm_shift_token(a, a.T - 1, red); }
@@ -380,6 +394,7 @@ __global__ void __launch_bounds__(256) k_norm_shift(const NormShiftArgs a) {
 // state (the last K-1 inputs of the sequence so far, oldest first; zeros at the start)
 struct ConvArgs { const float *v; uint32_t ldv; const float *taps, *bias; float *state; float *u; uint32_t T, C, K; };
 __global__ void k_conv(const ConvArgs a) {
+    pdl_enter();
     const size_t total = (size_t)a.T * a.C;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / a.C), c = (uint32_t)(i % a.C);
@@ -392,7 +407,9 @@ __global__ void k_conv(const ConvArgs a) {
         a.u[i] = s;
     }
 }
-__global__ void k_conv_state(const ConvArgs a) {     // after k_conv: the tail becomes the last K-1 inputs, this portion included
+// after k_conv: the tail becomes the last K-1 inputs, this portion included
+__global__ void k_conv_state(const ConvArgs a) {
+    pdl_enter();
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
     for (uint32_t j = 0; j + 1 < a.K; j++) {
@@ -403,6 +420,7 @@ __global__ void k_conv_state(const ConvArgs a) {     // after k_conv: the tail b
 
 // both steps in one launch for short portions: one thread per channel, tokens in order, then the tail
 __global__ void k_conv_small(const ConvArgs a) {
+    pdl_enter();
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
     for (uint32_t t = 0; t < a.T; t++) {
@@ -424,6 +442,7 @@ __global__ void k_conv_small(const ConvArgs a) {
 //   a = exp(-c_decay * r * softplus(lam)),  S <- a S + sqrt(1 - a^2) * (i * u),  out = S * y
 struct ScanArgs { const float *gates; uint32_t ldg; const float *u; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C; float c_decay; };
 __global__ void k_rglru_scan(const ScanArgs a) {
+    pdl_enter();
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
     const float sp = softplusf_(a.lam[c]);
@@ -442,6 +461,7 @@ __global__ void k_rglru_scan(const ScanArgs a) {
 // segment) first composes its segment's affine map S -> P S + Q, the segment-0 threads chain the maps to every segment's entry
 // state (and the portion's final state), then each thread replays its segment from its entry state and writes the outputs.
 __global__ void __launch_bounds__(1024) k_rglru_scan_par(const ScanArgs a) {
+    pdl_enter();
     __shared__ float P[32][33], Q[32][33];
     const uint32_t x = threadIdx.x, seg = threadIdx.y, nseg = blockDim.y, c = blockIdx.x * 32u + x;
     const uint32_t Ls = (a.T + nseg - 1u) / nseg, t0 = min(a.T, seg * Ls), t1 = min(a.T, t0 + Ls);
@@ -477,6 +497,7 @@ __global__ void __launch_bounds__(1024) k_rglru_scan_par(const ScanArgs a) {
 // key/value latent into the sequence's cache page of position pos0 + t
 struct LatentNormArgs { const float *z; uint32_t ldz; const float *wq, *wkv; float *cq; float *cache; const uint32_t *table; uint32_t QR, R, pos0; float eps; const uint32_t *pos_ptr; };
 __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
+    pdl_enter();
     __shared__ float red[32];
     const uint32_t t = blockIdx.x;
     const float *z = a.z + (size_t)t * a.ldz;
@@ -505,6 +526,7 @@ struct AttnArgs {
 };
 template <int RCH, int QT>
 __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
+    pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
     const uint32_t nq = min((uint32_t)QT, a.T - tq0);
@@ -635,6 +657,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
 // grid = (tokens, heads), block = 128: out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys.  The
 // (m, l) pairs of all splits are fetched at once (one per thread, nsplit <= 32), then the columns with every split's load in flight.
 __global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
+    pdl_enter();
     __shared__ float w_s[32]; __shared__ float L_s;
     const uint32_t t = blockIdx.x, h = blockIdx.y, R = a.R;
     const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
@@ -672,6 +695,7 @@ __global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
 // choice.  Dynamic shared memory: NE floats.
 struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E; };
 __global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
+    pdl_enter();
     extern __shared__ float z[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, t = blockIdx.x;
     const float *h = a.h + (size_t)t * a.E;
@@ -711,6 +735,7 @@ __global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
 // One block: off[e] = rows before expert e (off[NE] = total), counters cleared for the next use; then slot[t][j] = the row of
 // (token t, choice j) in the expert-sorted order and rows[slot] = t
 __global__ void __launch_bounds__(1024) k_route_place(const RouteArgs a) {
+    pdl_enter();
     if (threadIdx.x == 0) {
         uint32_t s = 0;
         for (uint32_t e = 0; e < a.NE; e++) { a.off[e] = s; s += a.counts[e]; a.counts[e] = 0; a.fill[e] = 0; }
@@ -727,6 +752,7 @@ __global__ void __launch_bounds__(1024) k_route_place(const RouteArgs a) {
 // x[t] += d[t] + ( sum_j wt[t][j] * eo[slot[t][j]]  (+ shared[t]) ),  the sum in the order of the choices; keep (optional) gets x
 struct CombineArgs { float *x; const float *d; const float *eo; const uint32_t *slot; const float *wt; const float *shared; float *keep; uint32_t T, E, top; };
 __global__ void k_combine(const CombineArgs a) {
+    pdl_enter();
     const size_t total = (size_t)a.T * a.E;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / a.E), c = (uint32_t)(i % a.E);
@@ -746,6 +772,7 @@ __global__ void k_combine(const CombineArgs a) {
 // scalar-gain RMS norm of the rows whose logits are asked for: out[i] = x[want[i]] / rms * g
 __global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x, const uint32_t *__restrict__ want, const float *__restrict__ g,
                                                     float *__restrict__ out, uint32_t E, float eps) {
+    pdl_enter();
     __shared__ float red[32];
     const float *xt = x + (size_t)want[blockIdx.x] * E;
     float s = 0.0f;
@@ -761,6 +788,7 @@ __global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x,
 // inside the prompt (pos + 1 < n_prompt); pos is read from (and advanced in) *pos_ptr when given.  penalised (optional) receives the logits after the penalty, for the sampler.
 struct PickArgs { float *logits; const uint8_t *seen; uint8_t *seen_rw; uint32_t *ids; uint32_t *next; uint32_t V, pos, n_prompt; float penalty; uint32_t advance; uint32_t *pos_ptr; };
 __global__ void __launch_bounds__(1024) k_pick(const PickArgs a) {
+    pdl_enter();
     __shared__ float bv[32]; __shared__ uint32_t bi[32];
     float best = -INFINITY; uint32_t idx = 0xffffffffu;
     for (uint32_t i = threadIdx.x; i < a.V; i += blockDim.x) {
@@ -789,6 +817,7 @@ __global__ void __launch_bounds__(1024) k_pick(const PickArgs a) {
     }
 }
 __global__ void k_mark(uint8_t *seen, const uint32_t *ids, uint32_t n) {
+    pdl_enter();
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) seen[ids[i]] = 1;
 }
 
