@@ -90,6 +90,7 @@ struct LayeredEngine : nb::EngineBase {
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
     float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
+    uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
     float *b_xn = nullptr, *logits = nullptr, *keep = nullptr;
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
@@ -269,15 +270,18 @@ int launch(LayeredEngine *e, void (*k)(const A), dim3 grid, dim3 block, size_t s
     return 0;
 }
 
-// one matrix product; maxM = the most rows any group can have.  wf32: the weights are fp32 whatever the engine's mode (router)
-int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32 = false) {
+uint32_t gemv_blocks(const LayeredEngine *e, uint32_t N, uint32_t groups) {
+    return std::min((N + 7u) / 8u, std::max(1u, (uint32_t)e->num_sms * 8u / groups));
+}
+
+// one matrix product; maxM = the most rows any group can have.  wf32: the weights are fp32 whatever the engine's mode (router).
+// active: how many of the groups can have rows at all (routed products: tokens x top); the matrix-vector grid is sized for those
+int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32 = false, uint32_t active = 0) {
     if (!a.a_gmod) a.a_gmod = 1;
     const bool f32 = e->f32 || wf32;
     if (maxM <= kGemvMaxM) {
         a.round_a = f32 ? 0u : 1u;
-        uint32_t gx = (a.N + 7u) / 8u;
-        const uint32_t cap = std::max(1u, (uint32_t)e->num_sms * 8u / groups);
-        gx = std::min(gx, cap);
+        const uint32_t gx = gemv_blocks(e, a.N, active ? std::min(active, groups) : groups);
         return f32 ? launch<GemmArgs>(e, k_gemv<float>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv<__nv_bfloat16>, dim3(gx, groups), dim3(256), 0, a);
     }
     const dim3 grid((a.N + 63u) / 64u, (maxM + 63u) / 64u, groups);
@@ -337,39 +341,52 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         }
         if (L.type == MIX_RGLRU) {
             const uint32_t C = L.C, bs = C / L.blocks;
-            if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
-            ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
-            if (T <= kGemvMaxM) { if ((r = launch<ConvArgs>(e, k_conv_small, dim3((C + 127) / 128), dim3(128), 0, ca))) return r; }
-            else {
+            if (T <= kGemvMaxM) {
+                // short portions: the convolution is the epilogue of the [y | x] product, gates and recurrence are one kernel
+                GemmArgs yx = plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_CONV, C);
+                yx.cv_taps = L.conv; yx.cv_bias = L.conv_b; yx.cv_state = st + run.st_conv; yx.cv_out = e->b_u; yx.cv_K = L.taps;
+                if ((r = gemm(e, yx, 1, T))) return r;
+                GatesScanArgs gs{e->b_u, L.gates.p, L.gates_b, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, bs, kRglruDecay, e->f32 ? 0u : 1u};
+                const dim3 grid((C + 7u) / 8u), block(256);
+                if ((r = e->f32 ? launch<GatesScanArgs>(e, k_rglru_gates_scan<float>, grid, block, 0, gs) : launch<GatesScanArgs>(e, k_rglru_gates_scan<__nv_bfloat16>, grid, block, 0, gs))) return r;
+            } else {
+                if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
+                ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
                 if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
                 if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
+                GemmArgs g{};
+                g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
+                g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
+                if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
+                ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
+                if (T <= 32) { if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r; }
+                else if ((r = launch<ScanArgs>(e, k_rglru_scan_par, dim3((C + 31) / 32), dim3(32, T >= 256 ? 32 : 8), 0, sa))) return r;
             }
-            GemmArgs g{};
-            g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
-            g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
-            if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
-            ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
-            if (T <= 32) { if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r; }
-            else if ((r = launch<ScanArgs>(e, k_rglru_scan_par, dim3((C + 31) / 32), dim3(32, T >= 256 ? 32 : 8), 0, sa))) return r;
             if ((r = gemm(e, plain(e->b_sy, C, L.o, e->d, E, T), 1, T))) return r;
         } else {
             const uint32_t H = L.H, R = L.R, QR = L.QR;
             if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
             LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
-            if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
-            if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+            if (T <= kGemvMaxM) {      // the norms ride on the query up-projection
+                GemvLatentArgs ga{plain(e->b_z, QR + R, L.uq, e->b_q, H * L.dim, T), na, T};
+                ga.g.a_norm_w = L.dq_norm; ga.g.a_eps = e->eps; ga.g.round_a = e->f32 ? 0u : 1u;
+                const dim3 grid(gemv_blocks(e, ga.g.N, 1)), block(256);
+                if ((r = e->f32 ? launch<GemvLatentArgs>(e, k_gemv_latent<float>, grid, block, 0, ga) : launch<GemvLatentArgs>(e, k_gemv_latent<__nv_bfloat16>, grid, block, 0, ga))) return r;
+            } else {
+                if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
+                if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+            }
             GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
             g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
             g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
             if ((r = gemm(e, g, H, T))) return r;
-            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr};
+            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr, e->b_tick};
             if (pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
             else if (T <= kGemvMaxM) {
                 const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
                 aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
             }
             if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
-            if (aa.nsplit > 1 && (r = launch<AttnArgs>(e, k_attn_merge, dim3(T, H), dim3(128), 0, aa))) return r;
             GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
             v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
             v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
@@ -383,16 +400,17 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
             e->cur = e->side;
             CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0));
             RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E};
-            if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), (size_t)L.NE * 4, ra)) ||
-                (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
+            if (T <= kGemvMaxM) { if ((r = launch<RouteArgs>(e, k_route_small, dim3(1), dim3(1024), route_smem(L.NE, 1024), ra))) return r; }
+            else if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), route_smem(L.NE, 256), ra)) ||
+                     (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
             GemmArgs u{};
             u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.C = e->b_hb; u.ldc = L.ff; u.M = T; u.N = L.ff; u.K = E; u.a_gmod = 1;
             u.g_off = e->b_off; u.a_rows = e->b_rows; u.w_gstride = (uint64_t)L.ff * E; u.epi = EPI_RELU2;
-            if ((r = gemm(e, u, L.NE, T))) return r;
+            if ((r = gemm(e, u, L.NE, T, false, T * L.top))) return r;
             GemmArgs dn{};
             dn.A = e->b_hb; dn.lda = L.ff; dn.W = L.down.p; dn.ldw = L.ff; dn.C = e->b_eo; dn.ldc = E; dn.M = T; dn.N = E; dn.K = L.ff; dn.a_gmod = 1;
             dn.g_off = e->b_off; dn.w_gstride = (uint64_t)E * L.ff;
-            if ((r = gemm(e, dn, L.NE, T))) return r;
+            if ((r = gemm(e, dn, L.NE, T, false, T * L.top))) return r;
             if (L.has_shared) {      // a third branch: the shared expert depends on h2 only
                 e->cur = e->side2;
                 CK(cudaStreamWaitEvent(e->side2, e->ev_fork, 0));
@@ -872,6 +890,10 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         uint32_t mPart = 0, mR = 0;
         for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.R); }
         DM(e->b_part, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
+        uint32_t mHG = 0;
+        for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) mHG = std::max(mHG, (L.H + kAttnWarps - 1) / kAttnWarps);
+        DM(e->b_tick, (size_t)kGemvMaxM * mHG * 4);
+        CK(cudaMemset(e->b_tick, 0, (size_t)kGemvMaxM * mHG * 4));
         if (attn_smem(mR, kAttnQT) > 48 * 1024 && (r = attn_optin<kAttnQT>((int)attn_smem(mR, kAttnQT)))) return r;
         if (attn_smem(mR, 4) > 48 * 1024 && (r = attn_optin<4>((int)attn_smem(mR, 4)))) return r;
         if (attn_smem(mR, 1) > 48 * 1024 && (r = attn_optin<1>((int)attn_smem(mR, 1)))) return r;

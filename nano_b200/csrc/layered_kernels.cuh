@@ -9,13 +9,16 @@
 //                        squared-relu epilogues.
 //   norms                k_norm_shift (RMS norm with ONE scalar gain, two gains of the same x at once, + token shift of the mixer's
 //                        input against the previous token's input, carried in the sequence state), k_latent_norm (vector-gain RMS norm
-//                        of the query latent and of the key/value latent, the latter written into the paged cache), k_final_norm
-//   recurrence           k_conv / k_conv_state / k_conv_small (causal per-channel convolution with its taps-1 tail in the state),
-//                        k_rglru_scan (real-gated linear recurrent unit: a = exp(-c r softplus(lam)), S = a S + sqrt(1 - a^2) i u, fp32
-//                        state; token by token) and k_rglru_scan_par (the same, parallel over time segments, for long portions)
+//                        of the query latent and of the key/value latent, the latter written into the paged cache; for short portions
+//                        k_gemv_latent does both inside the query up-projection), k_final_norm
+//   recurrence           k_conv / k_conv_state (causal per-channel convolution with its taps-1 tail in the state; for short portions it is
+//                        an epilogue of k_gemv), k_rglru_scan (real-gated linear recurrent unit: a = exp(-c r softplus(lam)),
+//                        S = a S + sqrt(1 - a^2) i u, fp32 state; token by token), k_rglru_scan_par (the same, parallel over time
+//                        segments, for long portions) and k_rglru_gates_scan (both gate products + the recurrence, short portions)
 //   attention            k_latent_attn (softmax attention of absorbed queries directly over cached latents: the latent is key AND
-//                        value, positions-free, causal; split over the keys for decode) + k_attn_merge
-//   mixture of experts   k_route (fp32 router logits -> top-k, softmax over the chosen), k_route_place (expert-sorted slots),
+//                        value, positions-free, causal; split over the keys for decode, merged by the block that finishes last)
+//   mixture of experts   k_route (fp32 router logits -> top-k, softmax over the chosen), k_route_place (expert-sorted slots), k_route_small
+//                        (both in one block, short portions),
 //                        k_combine (weighted sum in choice order + shared expert + mixer output -> residual)
 //
 // What is fp32 here regardless of the weight type: the residual stream, every norm, router logits, attention scores / weights /
@@ -33,7 +36,7 @@ constexpr uint32_t kPage = 32;            // tokens per cache page == keys per a
 constexpr uint32_t kAttnWarps = 8;        // heads per attention block
 constexpr uint32_t kGemvMaxM = 4;         // rows a k_gemv launch handles per group
 
-enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4 };
+enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5 };
 
 // C[r, c0 + n] = epi( sum_k A[arow(r), a0 + k] * W[g][n, k] + bias[g][n] )   for the rows r of group g
 //   rows of group g : [g_off[g], g_off[g+1])  when g_off is given (sizes known on the device only), else [0, M)
@@ -47,6 +50,12 @@ struct GemmArgs {
     uint64_t w_gstride;
     uint32_t epi, split;      // EPI_GELU_SPLIT: gelu_tanh on columns n < split, bias only on the others
     uint32_t round_a;         // k_gemv: round A to bf16 first (what the tensor-core kernel does to its operand)
+    // k_gemv only.  Prologue: when a_norm_w is given, row r of A is used as A[r, k] / rms(A[r, 0..K)) * a_norm_w[k] (eps inside the root).
+    const float *a_norm_w; float a_eps;
+    // k_gemv only.  Epilogue EPI_GELU_CONV: columns n < split get gelu_tanh and go to C; a column n >= split is channel c = n - split of a
+    // causal convolution over the rows in order (taps cv_taps[c][cv_K], bias cv_bias, tail cv_state [cv_K - 1][N - split]) whose
+    // outputs go to cv_out [rows][N - split]; the tail moves on.  One warp owns a channel, so the tail has one reader and one writer.
+    const float *cv_taps, *cv_bias; float *cv_state, *cv_out; uint32_t cv_K;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -66,7 +75,7 @@ __device__ __forceinline__ float softplusf_(float z) { return log1pf(expf(-fabsf
 __device__ __forceinline__ float epilogue(float v, const GemmArgs &a, const float *bias, uint32_t n) {
     if (bias) v += bias[n];
     switch (a.epi) {
-        case EPI_GELU_SPLIT: return n < a.split ? gelu_tanh(v) : v;
+        case EPI_GELU_SPLIT: case EPI_GELU_CONV: return n < a.split ? gelu_tanh(v) : v;
         case EPI_SIGMOID: return sigmoidf_(v);
         case EPI_RELU2: { const float r = fmaxf(v, 0.0f); return r * r; }
         default: return v;
@@ -265,9 +274,76 @@ template <> struct WVec<__nv_bfloat16> {
 };
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+__device__ __forceinline__ float block_sum(float v, float *red);
+
+__device__ __forceinline__ float pick_row(const float (&v)[kGemvMaxM], int32_t i) {
+    float x = v[0];
+#pragma unroll
+    for (int32_t j = 1; j < (int32_t)kGemvMaxM; j++) if (i == j) x = v[j];
+    return x;
+}
+// EPI_GELU_CONV for one channel c of C: v[t] is the channel's input at row t; outputs for the rows in order, then the tail moves on
+__device__ __forceinline__ void conv_rows(const GemmArgs &a, uint32_t c, uint32_t C, const float (&v)[kGemvMaxM], uint32_t rows, uint32_t r0) {
+    const uint32_t K = a.cv_K;
+    for (uint32_t t = 0; t < rows; t++) {
+        float s = a.cv_bias[c];
+        for (uint32_t j = 0; j < K; j++) {
+            const int32_t src = (int32_t)t - (int32_t)(K - 1u - j);
+            const float x = src >= 0 ? pick_row(v, src) : a.cv_state[(size_t)((int32_t)(K - 1u) + src) * C + c];
+            s = fmaf(a.cv_taps[(size_t)c * K + j], x, s);
+        }
+        a.cv_out[(size_t)(r0 + t) * C + c] = s;
+    }
+    for (uint32_t j = 0; j + 1u < K; j++) {
+        const int32_t src = (int32_t)rows - (int32_t)(K - 1u) + (int32_t)j;
+        a.cv_state[(size_t)j * C + c] = src >= 0 ? pick_row(v, src) : a.cv_state[(size_t)(j + rows) * C + c];
+    }
+}
+
+// dot products of one weight row with up to kGemvMaxM activation rows, summed over the warp's lanes: every lane returns the totals.
+// sc[i] / nw: the optional RMS-norm prologue (A[i][k] * sc[i] * nw[k]); rnd: round the activation to bf16 first.
 template <typename WT>
-__global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
-    pdl_enter();
+__device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemvMaxM], uint32_t rows, uint32_t K, uint32_t kvec, const float (&sc)[kGemvMaxM],
+                                          const float *nw, bool rnd, uint32_t lane, float (&acc)[kGemvMaxM]) {
+    constexpr uint32_t VN = WVec<WT>::N;
+#pragma unroll
+    for (uint32_t i = 0; i < kGemvMaxM; i++) acc[i] = 0.0f;
+#pragma unroll 4
+    for (uint32_t k = lane * VN; k < kvec; k += 32u * VN) {
+        float w[VN];
+        WVec<WT>::load(wr + k, w);
+#pragma unroll
+        for (uint32_t i = 0; i < kGemvMaxM; i++) {
+            if (i < rows) {
+#pragma unroll
+                for (uint32_t j = 0; j < VN; j += 4) {
+                    float4 x = *reinterpret_cast<const float4 *>(ap[i] + k + j);
+                    if (nw) { const float4 g = __ldg(reinterpret_cast<const float4 *>(nw + k + j)); x.x = x.x * sc[i] * g.x; x.y = x.y * sc[i] * g.y; x.z = x.z * sc[i] * g.z; x.w = x.w * sc[i] * g.w; }
+                    if (rnd) { x.x = round_bf16(x.x); x.y = round_bf16(x.y); x.z = round_bf16(x.z); x.w = round_bf16(x.w); }
+                    acc[i] = fmaf(w[j], x.x, acc[i]); acc[i] = fmaf(w[j + 1], x.y, acc[i]);
+                    acc[i] = fmaf(w[j + 2], x.z, acc[i]); acc[i] = fmaf(w[j + 3], x.w, acc[i]);
+                }
+            }
+        }
+    }
+    for (uint32_t k = kvec + lane; k < K; k += 32u) {
+        const float w = wval(wr + k);
+#pragma unroll
+        for (uint32_t i = 0; i < kGemvMaxM; i++)
+            if (i < rows) {
+                float x = ap[i][k];
+                if (nw) x = x * sc[i] * nw[k];
+                acc[i] = fmaf(w, rnd ? round_bf16(x) : x, acc[i]);
+            }
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < kGemvMaxM; i++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+}
+
+template <typename WT>
+__device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const GroupView gv = group_view(a, blockIdx.y);
     if (gv.rows == 0) return;
     const uint32_t rows = gv.rows < kGemvMaxM ? gv.rows : kGemvMaxM;
@@ -275,52 +351,48 @@ __global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
     const uint32_t warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = gridDim.x * (blockDim.x >> 5);
     const WT *W = static_cast<const WT *>(a.W) + gv.w0;
     const float *ap[kGemvMaxM];
+    float sc[kGemvMaxM];
     bool vec = (a.ldw % WVec<WT>::N == 0) && ((reinterpret_cast<uintptr_t>(W) & 15u) == 0);
 #pragma unroll
     for (uint32_t i = 0; i < kGemvMaxM; i++) {
         const uint32_t r = gv.r0 + (i < rows ? i : 0);
         ap[i] = a.A + (size_t)(a.a_rows ? a.a_rows[r] : r) * a.lda + gv.a0;
         vec = vec && ((reinterpret_cast<uintptr_t>(ap[i]) & 15u) == 0);
+        sc[i] = 1.0f;
     }
-    constexpr uint32_t VN = WVec<WT>::N;
-    const uint32_t kvec = vec ? (a.K / VN) * VN : 0u;
-    for (uint32_t n = warp0; n < a.N; n += nwarps) {
-        const WT *wr = W + (size_t)n * a.ldw;
-        float acc[kGemvMaxM] = {};
-        for (uint32_t k = lane * VN; k < kvec; k += 32u * VN) {
-            float w[VN];
-            WVec<WT>::load(wr + k, w);
+    if (a.a_norm_w) {          // rows is the same for every thread of the block
 #pragma unroll
-            for (uint32_t i = 0; i < kGemvMaxM; i++) {
-                if (i < rows) {
-#pragma unroll
-                    for (uint32_t j = 0; j < VN; j += 4) {
-                        const float4 x = *reinterpret_cast<const float4 *>(ap[i] + k + j);
-                        if (a.round_a) {
-                            acc[i] = fmaf(w[j], round_bf16(x.x), acc[i]); acc[i] = fmaf(w[j + 1], round_bf16(x.y), acc[i]);
-                            acc[i] = fmaf(w[j + 2], round_bf16(x.z), acc[i]); acc[i] = fmaf(w[j + 3], round_bf16(x.w), acc[i]);
-                        } else {
-                            acc[i] = fmaf(w[j], x.x, acc[i]); acc[i] = fmaf(w[j + 1], x.y, acc[i]);
-                            acc[i] = fmaf(w[j + 2], x.z, acc[i]); acc[i] = fmaf(w[j + 3], x.w, acc[i]);
-                        }
-                    }
-                }
+        for (uint32_t i = 0; i < kGemvMaxM; i++)
+            if (i < rows) {
+                float s = 0.0f;
+                for (uint32_t k = threadIdx.x; k < a.K; k += blockDim.x) s = fmaf(ap[i][k], ap[i][k], s);
+                s = block_sum(s, red);
+                sc[i] = 1.0f / sqrtf(s / (float)a.K + a.a_eps);
             }
-        }
-        for (uint32_t k = kvec + lane; k < a.K; k += 32u) {
-            const float w = wval(wr + k);
-#pragma unroll
-            for (uint32_t i = 0; i < kGemvMaxM; i++)
-                if (i < rows) { const float x = ap[i][k]; acc[i] = fmaf(w, a.round_a ? round_bf16(x) : x, acc[i]); }
-        }
-#pragma unroll
-        for (uint32_t i = 0; i < kGemvMaxM; i++) {
-            float v = acc[i];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && i < rows) a.C[(size_t)(gv.r0 + i) * a.ldc + gv.c0 + n] = epilogue(v, a, gv.bias, n);
-        }
     }
+    const uint32_t kvec = vec ? (a.K / WVec<WT>::N) * WVec<WT>::N : 0u;
+    for (uint32_t n = warp0; n < a.N; n += nwarps) {
+        float acc[kGemvMaxM];
+        warp_dots<WT>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc);
+        if (lane != 0) continue;
+        if (a.epi == EPI_GELU_CONV && n >= a.split) {
+            float v[kGemvMaxM];
+#pragma unroll
+            for (uint32_t i = 0; i < kGemvMaxM; i++) v[i] = acc[i] + (gv.bias ? gv.bias[n] : 0.0f);
+            conv_rows(a, n - a.split, a.N - a.split, v, rows, gv.r0);
+            continue;
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kGemvMaxM; i++)
+            if (i < rows) a.C[(size_t)(gv.r0 + i) * a.ldc + gv.c0 + n] = epilogue(acc[i], a, gv.bias, n);
+    }
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
+    pdl_enter();
+    __shared__ float red[32];
+    gemv_body<WT>(a, red);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -418,26 +490,6 @@ __global__ void k_conv_state(const ConvArgs a) {
     }
 }
 
-// both steps in one launch for short portions: one thread per channel, tokens in order, then the tail
-__global__ void k_conv_small(const ConvArgs a) {
-    pdl_enter();
-    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= a.C) return;
-    for (uint32_t t = 0; t < a.T; t++) {
-        float s = a.bias[c];
-        for (uint32_t j = 0; j < a.K; j++) {
-            const int64_t src = (int64_t)t - (int64_t)(a.K - 1 - j);
-            const float v = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)((int64_t)(a.K - 1) + src) * a.C + c];
-            s = fmaf(a.taps[(size_t)c * a.K + j], v, s);
-        }
-        a.u[(size_t)t * a.C + c] = s;
-    }
-    for (uint32_t j = 0; j + 1 < a.K; j++) {
-        const int64_t src = (int64_t)a.T - (int64_t)(a.K - 1) + j;
-        a.state[(size_t)j * a.C + c] = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)(j + a.T) * a.C + c];
-    }
-}
-
 // real-gated linear recurrent unit, one thread per channel, tokens in order:
 //   a = exp(-c_decay * r * softplus(lam)),  S <- a S + sqrt(1 - a^2) * (i * u),  out = S * y
 struct ScanArgs { const float *gates; uint32_t ldg; const float *u; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C; float c_decay; };
@@ -493,24 +545,82 @@ __global__ void __launch_bounds__(1024) k_rglru_scan_par(const ScanArgs a) {
     }
 }
 
+// Gates and recurrence of a short portion (<= kGemvMaxM tokens) in one launch: a warp per channel c of block b computes both gate
+// rows of its channel, r = sigmoid(ra[b][c] . u_b + bias) and i = sigmoid(ri[b][c] . u_b + bias), for every token, then runs the
+// recurrence of k_rglru_scan for that channel.  W = [ra blocks | ri blocks], each block [bs][bs]; bias likewise.
+struct GatesScanArgs { const float *u; const void *W; const float *bias; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C, bs; float c_decay; uint32_t round_a; };
+template <typename WT>
+__global__ void __launch_bounds__(256) k_rglru_gates_scan(const GatesScanArgs a) {
+    pdl_enter();
+    const uint32_t lane = threadIdx.x & 31u, c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (c >= a.C) return;
+    const uint32_t b = c / a.bs, rows = a.T < kGemvMaxM ? a.T : kGemvMaxM;
+    const WT *W = static_cast<const WT *>(a.W);
+    const WT *wr = W + (size_t)c * a.bs, *wi = W + (size_t)(a.C + c) * a.bs;
+    const float *ap[kGemvMaxM];
+    float sc[kGemvMaxM];
+    bool vec = (a.bs % WVec<WT>::N == 0) && ((reinterpret_cast<uintptr_t>(W) & 15u) == 0);
+#pragma unroll
+    for (uint32_t i = 0; i < kGemvMaxM; i++) {
+        ap[i] = a.u + (size_t)(i < rows ? i : 0) * a.C + (size_t)b * a.bs;
+        vec = vec && ((reinterpret_cast<uintptr_t>(ap[i]) & 15u) == 0);
+        sc[i] = 1.0f;
+    }
+    const uint32_t kvec = vec ? (a.bs / WVec<WT>::N) * WVec<WT>::N : 0u;
+    float gr[kGemvMaxM], gi[kGemvMaxM];
+    warp_dots<WT>(wr, ap, rows, a.bs, kvec, sc, nullptr, a.round_a != 0, lane, gr);
+    warp_dots<WT>(wi, ap, rows, a.bs, kvec, sc, nullptr, a.round_a != 0, lane, gi);
+    if (lane != 0) return;
+    const float sp = softplusf_(a.lam[c]), br = a.bias[c], bi = a.bias[a.C + c];
+    float S = a.S[c];
+#pragma unroll
+    for (uint32_t t = 0; t < kGemvMaxM; t++) {
+        if (t < rows) {
+            const float r = sigmoidf_(gr[t] + br), i = sigmoidf_(gi[t] + bi);
+            const float av = expf(-a.c_decay * r * sp);
+            S = av * S + sqrtf(1.0f - av * av) * (i * a.u[(size_t)t * a.C + c]);
+            a.out[(size_t)t * a.C + c] = S * a.y[(size_t)t * a.ldy + c];
+        }
+    }
+    a.S[c] = S;
+}
+
 // vector-gain RMS norms of the two latents of one token: z = [query latent | key/value latent]; the query latent goes to cq, the
 // key/value latent into the sequence's cache page of position pos0 + t
 struct LatentNormArgs { const float *z; uint32_t ldz; const float *wq, *wkv; float *cq; float *cache; const uint32_t *table; uint32_t QR, R, pos0; float eps; const uint32_t *pos_ptr; };
+// the key/value latent of token t: normed, into the cache page of its position
+__device__ __forceinline__ void latent_kv_row(const LatentNormArgs &a, uint32_t t, float *red) {
+    const float *z = a.z + (size_t)t * a.ldz + a.QR;
+    float s2 = 0.0f;
+    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) s2 = fmaf(z[i], z[i], s2);
+    s2 = block_sum(s2, red);
+    const float rk = 1.0f / sqrtf(s2 / (float)a.R + a.eps);
+    const uint32_t pos = a.pos0 + t + (a.pos_ptr ? *a.pos_ptr : 0u);
+    float *row = a.cache + ((size_t)a.table[pos / kPage] * kPage + pos % kPage) * a.R;
+    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) row[i] = z[i] * rk * a.wkv[i];
+}
 __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
     pdl_enter();
     __shared__ float red[32];
     const uint32_t t = blockIdx.x;
     const float *z = a.z + (size_t)t * a.ldz;
-    float s = 0.0f, s2 = 0.0f;
+    float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < a.QR; i += blockDim.x) s = fmaf(z[i], z[i], s);
-    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) s2 = fmaf(z[a.QR + i], z[a.QR + i], s2);
     s = block_sum(s, red);
-    s2 = block_sum(s2, red);
-    const float rq = 1.0f / sqrtf(s / (float)a.QR + a.eps), rk = 1.0f / sqrtf(s2 / (float)a.R + a.eps);
+    const float rq = 1.0f / sqrtf(s / (float)a.QR + a.eps);
     for (uint32_t i = threadIdx.x; i < a.QR; i += blockDim.x) a.cq[(size_t)t * a.QR + i] = z[i] * rq * a.wq[i];
-    const uint32_t pos = a.pos0 + t + (a.pos_ptr ? *a.pos_ptr : 0u);
-    float *row = a.cache + ((size_t)a.table[pos / kPage] * kPage + pos % kPage) * a.R;
-    for (uint32_t i = threadIdx.x; i < a.R; i += blockDim.x) row[i] = z[a.QR + i] * rk * a.wkv[i];
+    latent_kv_row(a, t, red);
+}
+// Short portions: the query latent's norm is the prologue of the query up-projection (GemmArgs::a_norm_w) and the last block of
+// that product also norms and caches the key/value latents, so the two norms cost no launch of their own.
+struct GemvLatentArgs { GemmArgs g; LatentNormArgs n; uint32_t T; };
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemv_latent(const GemvLatentArgs a) {
+    pdl_enter();
+    __shared__ float red[32];
+    if (blockIdx.x == gridDim.x - 1u && blockIdx.y == 0)
+        for (uint32_t t = 0; t < a.T; t++) latent_kv_row(a.n, t, red);
+    gemv_body<WT>(a.g, red);
 }
 
 // Softmax attention over cached latents.  qa[t][h][:] is head h's query already multiplied into latent space (q_h^T W_uk,h), so
@@ -519,10 +629,11 @@ __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
 // keys 0 .. pos + t, pos = pos0 (+ *pos_ptr in a captured decode step).
 // grid = (query tiles of QT tokens, key splits, head groups); one warp per head; lanes = keys for the scores, = latent columns for
 // the weighted sum; online softmax in fp32.  A key tile (one cache page) is fetched with all of a thread's 16-byte loads in flight
-// at once.  With one split the normalised result is written; otherwise partial (o, m, l) triples for k_attn_merge.
+// at once.  With one split the normalised result is written; otherwise partial (o, m, l) triples, merged at the end.
 struct AttnArgs {
     const float *qa; const float *cache; const uint32_t *table; float *out; float *part;
     uint32_t T, H, R, pos0, nsplit; float scale; const uint32_t *pos_ptr;
+    uint32_t *tickets;      // nsplit > 1: one zeroed counter per (query tile, head group); the block that draws the last ticket merges
 };
 template <int RCH, int QT>
 __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
@@ -637,10 +748,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
             }
         }
     }
-    if (h >= a.H) return;
 #pragma unroll
     for (int qi = 0; qi < QT; qi++) {
-        if ((uint32_t)qi >= nq) continue;
+        if ((uint32_t)qi >= nq || h >= a.H) continue;
         const uint32_t t = tq0 + qi;
         if (a.nsplit == 1) {
             const float inv = 1.0f / l[qi];
@@ -653,20 +763,31 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
             if (lane == 0) { dst[R] = m[qi]; dst[R + 1] = l[qi]; }
         }
     }
-}
-// grid = (tokens, heads), block = 128: out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits that saw keys.  The
-// (m, l) pairs of all splits are fetched at once (one per thread, nsplit <= 32), then the columns with every split's load in flight.
-__global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
-    pdl_enter();
-    __shared__ float w_s[32]; __shared__ float L_s;
-    const uint32_t t = blockIdx.x, h = blockIdx.y, R = a.R;
-    const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
+    if (a.nsplit == 1) return;
+    // Key splits: every block has written partial (o, m, l) triples.  The block that draws the last ticket of its (query tile, head
+    // group) sees all of them (fence before the ticket, fence after) and merges:
+    //   out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s   over the splits that saw keys.
+    __shared__ uint32_t last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t *tk = a.tickets + blockIdx.x * gridDim.z + blockIdx.z;
+        const uint32_t got = atomicAdd(tk, 1u);
+        last_s = got + 1u == a.nsplit;
+        if (last_s) *tk = 0u;              // ready for the next launch
+    }
+    __syncthreads();
+    if (!last_s || h >= a.H) return;
+    __threadfence();
     const size_t stride = (size_t)a.H * (R + 2u);
-    if (threadIdx.x < 32) {
-        const uint32_t s = threadIdx.x;
-        const bool live = s < a.nsplit;
-        const float ls = live ? base[s * stride + R + 1] : 0.0f;
-        const float ms = (live && ls > 0.0f) ? base[s * stride + R] : -INFINITY;
+#pragma unroll
+    for (int qi = 0; qi < QT; qi++) {
+        if ((uint32_t)qi >= nq) continue;
+        const uint32_t t = tq0 + qi;
+        const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
+        const bool live = lane < a.nsplit;
+        const float ls = live ? __ldcg(base + lane * stride + R + 1u) : 0.0f;
+        const float ms = (live && ls > 0.0f) ? __ldcg(base + lane * stride + R) : -INFINITY;
         float M = ms;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
@@ -674,16 +795,19 @@ __global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
         float L = w * ls;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-        w_s[s] = w;
-        if (s == 0) L_s = L;
-    }
-    __syncthreads();
-    const float inv = 1.0f / L_s;
-    for (uint32_t r = threadIdx.x; r < R; r += blockDim.x) {
-        float acc = 0.0f;
-#pragma unroll 8
-        for (uint32_t s = 0; s < a.nsplit; s++) acc = fmaf(w_s[s], w_s[s] > 0.0f ? base[s * stride + r] : 0.0f, acc);
-        a.out[((size_t)t * a.H + h) * R + r] = acc * inv;
+        float acc[RCH];
+#pragma unroll
+        for (int c = 0; c < RCH; c++) acc[c] = 0.0f;
+        // every split wrote its triple in this launch (zeros where it saw no key), so the loop needs no branch and its loads overlap
+#pragma unroll 4
+        for (uint32_t s = 0; s < a.nsplit; s++) {
+            const float ws = __shfl_sync(0xffffffffu, w, s);
+#pragma unroll
+            for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) acc[c] = fmaf(ws, __ldcg(base + s * stride + r), acc[c]); }
+        }
+        const float inv = 1.0f / L;
+#pragma unroll
+        for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) a.out[((size_t)t * a.H + h) * R + r] = acc[c] * inv; }
     }
 }
 
@@ -692,31 +816,44 @@ __global__ void __launch_bounds__(128) k_attn_merge(const AttnArgs a) {
 // ------------------------------------------------------------------------------------------------
 // One block per token: router logits z_e = W_router[e] . h in fp32 (a warp per expert, lanes stride over the width), then the
 // `top` largest (ties: the lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per
-// choice.  Dynamic shared memory: NE floats.
+// choice.  Dynamic shared memory: route_smem(NE, threads) bytes.
 struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E; };
-__global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
-    pdl_enter();
-    extern __shared__ float z[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, t = blockIdx.x;
+// dynamic shared memory of k_route / k_route_small launched with `threads` threads
+inline size_t route_smem(uint32_t NE, uint32_t threads) { const uint32_t nw = threads / 32u; return ((size_t)NE + (size_t)NE * (nw > NE ? nw / NE : 1u)) * 4; }
+// router logits of token t into z[NE].  The blockDim/32 warps are dealt out as `ns` slices per expert (ns = warps / NE, at least 1):
+// a warp sums its slice of the row, the slices are added in order.  zp: NE * ns floats of scratch.
+__device__ __forceinline__ uint32_t route_slices(uint32_t NE) { const uint32_t nw = blockDim.x >> 5; return nw > NE ? nw / NE : 1u; }
+__device__ __forceinline__ void route_logits(const RouteArgs &a, uint32_t t, float *z, float *zp) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nw = blockDim.x >> 5, ns = route_slices(a.NE);
     const float *h = a.h + (size_t)t * a.E;
     const bool vec = (a.E % 4u) == 0;
-    for (uint32_t e = warp; e < a.NE; e += blockDim.x >> 5) {
+    const uint32_t per = ((a.E + ns - 1u) / ns + 3u) & ~3u;          // slice length, a multiple of 4
+    for (uint32_t job = warp; job < a.NE * ns; job += nw) {
+        const uint32_t e = job / ns, sl = job % ns;
+        const uint32_t k0 = min(a.E, sl * per), k1 = min(a.E, k0 + per);
         const float *w = a.router + (size_t)e * a.E;
         float acc = 0.0f;
         if (vec) {
-            for (uint32_t k = lane * 4u; k < a.E; k += 128u) {
+            for (uint32_t k = k0 + lane * 4u; k < k1; k += 128u) {
                 const float4 hv = *reinterpret_cast<const float4 *>(h + k), wv = __ldg(reinterpret_cast<const float4 *>(w + k));
                 acc = fmaf(hv.w, wv.w, fmaf(hv.z, wv.z, fmaf(hv.y, wv.y, fmaf(hv.x, wv.x, acc))));
             }
         } else {
-            for (uint32_t k = lane; k < a.E; k += 32u) acc = fmaf(h[k], w[k], acc);
+            for (uint32_t k = k0 + lane; k < k1; k += 32u) acc = fmaf(h[k], w[k], acc);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) z[e] = acc;
+        if (lane == 0) zp[job] = acc;
     }
     __syncthreads();
-    if (threadIdx.x) return;
+    for (uint32_t e = threadIdx.x; e < a.NE; e += blockDim.x) {
+        float v = 0.0f;
+        for (uint32_t sl = 0; sl < ns; sl++) v += zp[e * ns + sl];
+        z[e] = v;
+    }
+}
+// one thread: the `top` largest of z (ties: the lower index first; z is consumed) and the softmax over them
+__device__ __forceinline__ void route_pick(const RouteArgs &a, uint32_t t, float *z) {
     uint32_t *idx = a.idx + (size_t)t * a.top; float *wt = a.wt + (size_t)t * a.top;
     for (uint32_t j = 0; j < a.top; j++) {
         float best = -INFINITY; uint32_t bi = 0xffffffffu;
@@ -730,7 +867,37 @@ __global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
     const float mx = wt[0];
     float s = 0.0f;
     for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - mx); s += wt[j]; }
-    for (uint32_t j = 0; j < a.top; j++) { wt[j] /= s; atomicAdd(a.counts + idx[j], 1u); }
+    for (uint32_t j = 0; j < a.top; j++) wt[j] /= s;
+}
+__global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
+    pdl_enter();
+    extern __shared__ float z[];
+    route_logits(a, blockIdx.x, z, z + a.NE);
+    __syncthreads();
+    if (threadIdx.x) return;
+    route_pick(a, blockIdx.x, z);
+    for (uint32_t j = 0; j < a.top; j++) atomicAdd(a.counts + a.idx[(size_t)blockIdx.x * a.top + j], 1u);
+}
+// Short portions: routing and placement of all T tokens in one block of 1024 threads (the one block has the router matrix to itself,
+// so every warp fetches).  Same outputs as k_route + k_route_place; the global counters are not touched.
+__global__ void __launch_bounds__(1024) k_route_small(const RouteArgs a) {
+    pdl_enter();
+    extern __shared__ float z[];
+    uint32_t *cur = reinterpret_cast<uint32_t *>(z);          // after the last token z is free
+    for (uint32_t t = 0; t < a.T; t++) {
+        route_logits(a, t, z, z + a.NE);
+        __syncthreads();
+        if (threadIdx.x == 0) route_pick(a, t, z);
+        __syncthreads();
+    }
+    if (threadIdx.x) return;
+    const uint32_t n = a.T * a.top;
+    for (uint32_t e = 0; e < a.NE; e++) cur[e] = 0;
+    for (uint32_t i = 0; i < n; i++) cur[a.idx[i]]++;
+    uint32_t s = 0;
+    for (uint32_t e = 0; e < a.NE; e++) { const uint32_t c = cur[e]; a.off[e] = s; cur[e] = s; s += c; }
+    a.off[a.NE] = s;
+    for (uint32_t i = 0; i < n; i++) { const uint32_t sl = cur[a.idx[i]]++; a.slot[i] = sl; a.rows[sl] = i / a.top; }
 }
 // One block: off[e] = rows before expert e (off[NE] = total), counters cleared for the next use; then slot[t][j] = the row of
 // (token t, choice j) in the expert-sorted order and rows[slot] = t

@@ -300,3 +300,30 @@ def test_other_families_refuse_cleanly(tmp_path):
     with pytest.raises(E.NB200Error, match="Nano family"):
         eng.run_layer(0, 0)
     eng.close()
+
+
+# ---- the replay command: token steps on standard input, logits files out, through the same engine calls ----
+def test_trace_replay_command(tmp_path):
+    import json, subprocess, sys
+    cfg = mixed_cfg(vocab=70)
+    w = md.famudra_random(cfg, 4)
+    path = md.write_model_dir(str(tmp_path / "m"), cfg, w)
+    ta, tb = toks(cfg, 50, 21), toks(cfg, 9, 22)
+    ra, rb = oracle_forward(cfg, w, ta, np.float64), oracle_forward(cfg, w, tb, np.float64)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": ta[:33].tolist(), "want": [32, 0, 5]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": ta[33:35].tolist(), "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": ta[35:36].tolist(), "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": ta[36:50].tolist(), "want": [13]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "b", "tokens": tb.tolist(), "want": [8, 7]}], "end": ["b"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype, tol in (("float32", F32_TOL), ("bfloat16", BF16_TOL)):
+        out = tmp_path / ("out_" + dtype)
+        p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", str(out), "--max-tokens", "64"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == ["done %d" % i for i in range(5)]
+        got = {i: np.fromfile(out / ("%d.f32" % i), "<f4").reshape(-1, cfg["vocab"]) for i in (0, 2, 3, 4)}
+        assert not (out / "1.f32").exists()
+        assert rel(got[0], ra[[32, 0, 5]]) < tol                      # in the order "want" lists them
+        assert rel(got[2], ra[[35]]) < tol and rel(got[3], ra[[49]]) < tol
+        assert rel(got[4], rb[[8, 7]]) < tol
