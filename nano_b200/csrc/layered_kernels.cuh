@@ -651,9 +651,20 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
     const uint32_t nkeys = pos + tq0 + nq, tiles = (nkeys + kPage - 1u) / kPage;      // keys of the block's last query
     const uint32_t tps = (tiles + a.nsplit - 1u) / a.nsplit;
     const uint32_t tile_lo = split * tps, tile_hi = min(tiles, tile_lo + tps);
-    for (uint32_t i = threadIdx.x; i < QT * kAttnWarps * R; i += blockDim.x) {
-        const uint32_t qi = i / (kAttnWarps * R), rem = i % (kAttnWarps * R), hh = h0 + rem / R;
-        q_s[i] = (qi < nq && hh < a.H) ? a.qa[((size_t)(tq0 + qi) * a.H + hh) * R + rem % R] : 0.0f;
+    if (vec) {          // a query token's kAttnWarps heads are contiguous in qa: 16-byte copies, all of a thread's loads in flight
+        const uint32_t per = kAttnWarps * R / 4u, live = (min(a.H, h0 + kAttnWarps) - h0) * R / 4u;
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < QT * per; i += blockDim.x) {
+            const uint32_t qi = i / per, rem = i % per;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (qi < nq && rem < live) v = *(reinterpret_cast<const float4 *>(a.qa + ((size_t)(tq0 + qi) * a.H + h0) * R) + rem);
+            reinterpret_cast<float4 *>(q_s)[i] = v;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < QT * kAttnWarps * R; i += blockDim.x) {
+            const uint32_t qi = i / (kAttnWarps * R), rem = i % (kAttnWarps * R), hh = h0 + rem / R;
+            q_s[i] = (qi < nq && hh < a.H) ? a.qa[((size_t)(tq0 + qi) * a.H + hh) * R + rem % R] : 0.0f;
+        }
     }
     float m[QT], l[QT], o[QT][RCH];
 #pragma unroll
@@ -695,15 +706,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
         for (int qi = 0; qi < QT; qi++) sc[qi] = 0.0f;
         const float *cr = c_s + lane * LDC;         // lanes past nk read rows of an earlier tile: their scores are masked below
         if (vec) {
+            float sc4[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // a single query: four independent partial sums instead of one long chain
             const float4 *c4 = reinterpret_cast<const float4 *>(cr);
             for (uint32_t r4 = 0; r4 < R / 4u; r4++) {
                 const float4 cv = c4[r4];
 #pragma unroll
                 for (int qi = 0; qi < QT; qi++) {
                     const float4 qv = reinterpret_cast<const float4 *>(q_s + ((size_t)qi * kAttnWarps + warp) * R)[r4];
-                    sc[qi] = fmaf(qv.w, cv.w, fmaf(qv.z, cv.z, fmaf(qv.y, cv.y, fmaf(qv.x, cv.x, sc[qi]))));
+                    if (QT == 1) { sc4[0] = fmaf(qv.x, cv.x, sc4[0]); sc4[1] = fmaf(qv.y, cv.y, sc4[1]); sc4[2] = fmaf(qv.z, cv.z, sc4[2]); sc4[3] = fmaf(qv.w, cv.w, sc4[3]); }
+                    else sc[qi] = fmaf(qv.w, cv.w, fmaf(qv.z, cv.z, fmaf(qv.y, cv.y, fmaf(qv.x, cv.x, sc[qi]))));
                 }
             }
+            if (QT == 1) sc[0] = (sc4[0] + sc4[1]) + (sc4[2] + sc4[3]);
         } else {
             for (uint32_t r = 0; r < R; r++) {
                 const float cv = cr[r];
@@ -780,12 +794,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
     if (!last_s || h >= a.H) return;
     __threadfence();
     const size_t stride = (size_t)a.H * (R + 2u);
+    const uint32_t nact = min(a.nsplit, (tiles + tps - 1u) / tps);      // splits that own key tiles; the others wrote nothing of weight
 #pragma unroll
     for (int qi = 0; qi < QT; qi++) {
         if ((uint32_t)qi >= nq) continue;
         const uint32_t t = tq0 + qi;
         const float *base = a.part + ((size_t)t * a.nsplit * a.H + h) * (R + 2u);
-        const bool live = lane < a.nsplit;
+        const bool live = lane < nact;
         const float ls = live ? __ldcg(base + lane * stride + R + 1u) : 0.0f;
         const float ms = (live && ls > 0.0f) ? __ldcg(base + lane * stride + R) : -INFINITY;
         float M = ms;
@@ -798,9 +813,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs 
         float acc[RCH];
 #pragma unroll
         for (int c = 0; c < RCH; c++) acc[c] = 0.0f;
-        // every split wrote its triple in this launch (zeros where it saw no key), so the loop needs no branch and its loads overlap
+        // every one of these splits wrote its triple in this launch (zeros where no key was visible to this query), so the loop needs
+        // no branch and its loads overlap
 #pragma unroll 4
-        for (uint32_t s = 0; s < a.nsplit; s++) {
+        for (uint32_t s = 0; s < nact; s++) {
             const float ws = __shfl_sync(0xffffffffu, w, s);
 #pragma unroll
             for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) acc[c] = fmaf(ws, __ldcg(base + s * stride + r), acc[c]); }

@@ -79,6 +79,14 @@ def test_mixer_alone(tmp_path, kind, mixer):
     res = eng.read_residual(0, len(t))
     assert np.abs(res - trace[0]).max() <= 2e-5 * np.abs(trace[0]).max()
     assert rel(got, ref) < F32_TOL
+    for cuts in ([1] * 45, [2, 3, 4] * 5):                  # the short-portion kernels of the same mechanism
+        s = eng.seq_open()
+        out, at = [], 0
+        for c in cuts:
+            out.append(eng.step(s, t[at:at + c], range(c)))
+            at += c
+        eng.seq_close(s)
+        assert rel(np.concatenate(out), ref) < F32_TOL, cuts[:3]
     eng.close()
 
 
