@@ -483,7 +483,7 @@ def tp_block(E, rank, world, local, dist):
 # --------------------------------------------------------------------------------------------------
 # --design famudra: prefill and decode throughput of the layered family at layer sizes of real models (random weights), beside the
 # closest model the engine had before it -- a Qwen3-architecture Q80 model file of the same width and depth.  Not the default
-# workload: the headline line and its contract are untouched.
+# workload: the headline line and its format are untouched.
 # --------------------------------------------------------------------------------------------------
 FAMUDRA_SIZES = {
     # name: (width, layers, recurrent width / blocks, heads, dim, vdim, kv_rank, q_rank, experts, top, expert ff, shared ff, peer hidden)
