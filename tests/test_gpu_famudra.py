@@ -302,6 +302,17 @@ def test_sampled_generation_and_penalty(tmp_path):
     eng.close()
 
 
+def test_single_number_gains_stored_as_vectors_of_one(tmp_path):
+    cfg = md.famudra_config(40, 32, [("rglru", {"width": 16, "blocks": 1, "conv": 2}, {"experts": 2, "top": 1, "ff": 8, "shared_ff": None})])
+    w = md.famudra_random(cfg, 3)
+    w1 = {k: (np.reshape(v, (1,)) if np.ndim(v) == 0 else v) for k, v in w.items()}
+    path = md.write_model_dir(str(tmp_path / "v1"), cfg, w1)
+    eng = E.Engine(path, 64, flags=E.FLAG_F32)
+    t = toks(cfg, 12)
+    assert rel(whole(eng, t), oracle_forward(cfg, w, t, np.float64)) < F32_TOL
+    eng.close()
+
+
 def test_other_families_refuse_cleanly(tmp_path):
     cfg = md.famudra_config(40, 32, [("rglru", {"width": 16, "blocks": 1, "conv": 2}, None)])
     eng, _ = build(tmp_path, cfg)
