@@ -303,25 +303,33 @@ uint32_t ew_grid(size_t n) { return (uint32_t)std::min<size_t>((n + 255) / 256, 
 constexpr int kAttnQT = 8;      // query tokens per attention block in a prefill portion (4 where the latent is wider than 256)
 size_t attn_smem(uint32_t R, int qt) { return ((size_t)qt * kAttnWarps * R + (size_t)kPage * (R + 4)) * 4; }
 
+template <int RCH, int QT>
+int attn_launch_r(LayeredEngine *e, const AttnArgs &a, dim3 grid, dim3 block, size_t smem) {
+    return a.R == (uint32_t)RCH * 32u ? launch<AttnArgs>(e, k_latent_attn<RCH, QT, true>, grid, block, smem, a) : launch<AttnArgs>(e, k_latent_attn<RCH, QT, false>, grid, block, smem, a);
+}
 template <int QT>
 int attn_launch_qt(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
     const dim3 grid((a.T + QT - 1) / QT, a.nsplit, (a.H + kAttnWarps - 1) / kAttnWarps), block(kAttnWarps * 32);
     const size_t smem = attn_smem(a.R, QT);
-    if (rch <= 2) return launch<AttnArgs>(e, k_latent_attn<2, QT>, grid, block, smem, a);
-    if (rch <= 4) return launch<AttnArgs>(e, k_latent_attn<4, QT>, grid, block, smem, a);
-    if (rch <= 8) return launch<AttnArgs>(e, k_latent_attn<8, QT>, grid, block, smem, a);
-    return launch<AttnArgs>(e, k_latent_attn<16, QT>, grid, block, smem, a);
+    if (rch <= 2) return attn_launch_r<2, QT>(e, a, grid, block, smem);
+    if (rch <= 4) return attn_launch_r<4, QT>(e, a, grid, block, smem);
+    if (rch <= 8) return attn_launch_r<8, QT>(e, a, grid, block, smem);
+    return attn_launch_r<16, QT>(e, a, grid, block, smem);
 }
 int attn_launch(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
     if (a.T <= kGemvMaxM) return attn_launch_qt<1>(e, a, rch);
     return rch <= 8 ? attn_launch_qt<kAttnQT>(e, a, rch) : attn_launch_qt<4>(e, a, rch);
 }
+template <int RCH, int QT>
+int attn_optin_r(int smem) {
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    return 0;
+}
 template <int QT>
 int attn_optin(int smem) {
-    CK(cudaFuncSetAttribute((const void *)k_latent_attn<2, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    CK(cudaFuncSetAttribute((const void *)k_latent_attn<4, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    CK(cudaFuncSetAttribute((const void *)k_latent_attn<8, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    CK(cudaFuncSetAttribute((const void *)k_latent_attn<16, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    int r;
+    if ((r = attn_optin_r<2, QT>(smem)) || (r = attn_optin_r<4, QT>(smem)) || (r = attn_optin_r<8, QT>(smem)) || (r = attn_optin_r<16, QT>(smem))) return r;
     return 0;
 }
 

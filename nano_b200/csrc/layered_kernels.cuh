@@ -635,14 +635,16 @@ struct AttnArgs {
     uint32_t T, H, R, pos0, nsplit; float scale; const uint32_t *pos_ptr;
     uint32_t *tickets;      // nsplit > 1: one zeroed counter per (query tile, head group); the block that draws the last ticket merges
 };
-template <int RCH, int QT>
+// EXACT: the latent rank is RCH * 32 (64, 128, 256, 512): R is a compile-time constant, so row offsets are immediates, the
+// divisions of the staging loops are shifts and the column guards vanish.
+template <int RCH, int QT, bool EXACT>
 __global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
     const uint32_t nq = min((uint32_t)QT, a.T - tq0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = h0 + warp;
-    const uint32_t R = a.R;
+    const uint32_t R = EXACT ? (uint32_t)RCH * 32u : a.R;
     const bool vec = (R % 4u) == 0;                // 16-byte shared-memory rows: (R + 4) / 4 is odd for R % 8 == 0, so 8 lanes hit 8 bank groups
     const uint32_t LDC = vec ? R + 4u : R + 1u;
     float *q_s = sm;                               // [QT][kAttnWarps][R]

@@ -68,7 +68,11 @@ def whole(eng, t, want=None):
 # ---- each mechanism alone: one layer, no feed-forward, residual after the layer and logits ----
 @pytest.mark.parametrize("kind,mixer", [("rglru", REC), ("rglru", {"width": 64, "blocks": 1, "conv": 1}), ("rglru", {"width": 80, "blocks": 5, "conv": 2}),
                                         ("latent_attention", ATT), ("latent_attention", {"heads": 1, "dim": 16, "vdim": 8, "kv_rank": 20, "q_rank": 12, "scale": 0.5}),
-                                        ("latent_attention", {"heads": 10, "dim": 8, "vdim": 8, "kv_rank": 96, "q_rank": 32, "scale": 0.3})])
+                                        ("latent_attention", {"heads": 10, "dim": 8, "vdim": 8, "kv_rank": 96, "q_rank": 32, "scale": 0.3}),
+                                        # latent ranks of 64 / 128 / 256 take the attention kernel's compile-time-rank instances
+                                        ("latent_attention", {"heads": 4, "dim": 8, "vdim": 12, "kv_rank": 64, "q_rank": 24, "scale": 0.4}),
+                                        ("latent_attention", {"heads": 9, "dim": 12, "vdim": 8, "kv_rank": 128, "q_rank": 20, "scale": 0.3}),
+                                        ("latent_attention", {"heads": 2, "dim": 8, "vdim": 8, "kv_rank": 256, "q_rank": 16, "scale": 0.2})])
 def test_mixer_alone(tmp_path, kind, mixer):
     cfg = md.famudra_config(61, 72, [(kind, mixer, None)])
     eng, w = build(tmp_path, cfg, keep=True)
