@@ -96,6 +96,7 @@ struct LayeredEngine : nb::EngineBase {
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
     uint32_t *dpos = nullptr, *zero_dev = nullptr;            // device-side position of a captured decode step; a constant 0
+    bool branch_streams = true;      // a layer's feed-forward and shared expert on streams of their own (NB200_NO_BRANCH_STREAMS=1: one stream)
     bool use_pdl = true; bool use_graph = true; std::vector<cudaGraphExec_t> graphs; uint32_t graph_launches = 0;
     // generation on the implicit sequence
     int gen_seq = -1;
@@ -348,7 +349,7 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         {
             NormShiftArgs a{e->x, L.norm1, L.has_mlp ? L.norm2 : nullptr, L.shift, st + run.st_prev, e->hm, L.has_mlp ? e->h2 : nullptr, T, E, e->eps};
             if ((r = launch<NormShiftArgs>(e, k_norm_shift, dim3(T > 1 ? T - 1 : 1), dim3(256), 0, a))) return r;
-            if (L.has_mlp) CK(cudaEventRecord(e->ev_fork, e->stream));
+            if (L.has_mlp && e->branch_streams) CK(cudaEventRecord(e->ev_fork, e->stream));
         }
         if (L.type == MIX_RGLRU) {
             const uint32_t C = L.C, bs = C / L.blocks;
@@ -408,8 +409,7 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         if (L.has_mlp) {
             // The layer is parallel: the feed-forward reads h2 = norm2(x) of the SAME x and shares no buffer with the mixer, so its
             // kernels go to a second stream (a parallel branch of the captured decode graph) and join before the residual update.
-            e->cur = e->side;
-            CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0));
+            if (e->branch_streams) { e->cur = e->side; CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0)); }
             RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E};
             if (T <= kGemvMaxM) { if ((r = launch<RouteArgs>(e, k_route_small, dim3(1), dim3(1024), route_smem(L.NE, 1024), ra))) return r; }
             else if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), route_smem(L.NE, 256), ra)) ||
@@ -423,16 +423,13 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
             dn.g_off = e->b_off; dn.w_gstride = (uint64_t)E * L.ff;
             if ((r = gemm(e, dn, L.NE, T, false, T * L.top))) return r;
             if (L.has_shared) {      // a third branch: the shared expert depends on h2 only
-                e->cur = e->side2;
-                CK(cudaStreamWaitEvent(e->side2, e->ev_fork, 0));
+                if (e->branch_streams) { e->cur = e->side2; CK(cudaStreamWaitEvent(e->side2, e->ev_fork, 0)); }
                 if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, L.sff, T, nullptr, EPI_RELU2), 1, T)) || (r = gemm(e, plain(e->b_sh, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
-                CK(cudaEventRecord(e->ev_join2, e->side2));
-                CK(cudaStreamWaitEvent(e->stream, e->ev_join2, 0));
+                if (e->branch_streams) { CK(cudaEventRecord(e->ev_join2, e->side2)); CK(cudaStreamWaitEvent(e->stream, e->ev_join2, 0)); }
             }
             c.eo = e->b_eo; c.slot = e->b_slot; c.wt = e->b_wt; c.shared = L.has_shared ? e->b_so : nullptr; c.top = L.top;
             e->cur = e->stream;
-            CK(cudaEventRecord(e->ev_join, e->side));
-            CK(cudaStreamWaitEvent(e->stream, e->ev_join, 0));
+            if (e->branch_streams) { CK(cudaEventRecord(e->ev_join, e->side)); CK(cudaStreamWaitEvent(e->stream, e->ev_join, 0)); }
         }
         if ((r = launch<CombineArgs>(e, k_combine, dim3(ew_grid((size_t)T * E)), dim3(256), 0, c))) return r;
     }
@@ -938,6 +935,7 @@ extern "C" int nb_family_layered_create(nb200_engine **out, const nb::ModelDir *
     e->device = device; e->f32 = (flags & NB200_FLAG_F32) != 0;
     e->use_pdl = !(flags & NB200_FLAG_NO_PDL) && !env_u32("NB200_NO_PDL", 0);
     e->use_graph = !(flags & NB200_FLAG_NO_GRAPH) && !env_u32("NB200_NO_GRAPH", 0);
+    e->branch_streams = !env_u32("NB200_NO_BRANCH_STREAMS", 0);
     cudaDeviceProp prop;
     cudaError_t ce = cudaGetDeviceProperties(&prop, device);
     if (ce == cudaSuccess) { e->num_sms = prop.multiProcessorCount; ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking); }

@@ -637,8 +637,13 @@ struct AttnArgs {
 };
 // EXACT: the latent rank is RCH * 32 (64, 128, 256, 512): R is a compile-time constant, so row offsets are immediates, the
 // divisions of the staging loops are shifts and the column guards vanish.
+// Two blocks per SM (128 registers) where the shared memory of a prefill instance fits twice; measured faster at rank 256 with 8 queries,
+// slower where the second block cannot be resident anyway (rank 512).
+constexpr bool attn_two_blocks(int rch, int qt, bool exact) {
+    return exact && qt > 1 && ((size_t)qt * kAttnWarps * rch * 32 + (size_t)kPage * (rch * 32 + 4)) * 4 <= 112u * 1024u;
+}
 template <int RCH, int QT, bool EXACT>
-__global__ void __launch_bounds__(kAttnWarps * 32) k_latent_attn(const AttnArgs a) {
+__global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXACT) ? 2 : 1) k_latent_attn(const AttnArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
