@@ -60,10 +60,20 @@ struct GemmArgs {
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
 // pdl_enter until this grid has finished and its writes are visible), then waits for the kernels before it.  Launch latency and block
-// scheduling of a chain of short kernels overlap with the tail of the kernel before; no kernel touches global memory before the wait.
-__device__ __forceinline__ void pdl_enter() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+// scheduling of a chain of short kernels overlap with the tail of the kernel before; no kernel reads or writes what another kernel
+// produces before the wait (weights may be prefetched: nothing writes them).
+__device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_launch_next(); pdl_wait(); }
+// Weights do not depend on the kernel before: a matrix-vector kernel asks for its weight rows (L2 prefetch, no register, no wait)
+// BETWEEN the two halves of pdl_enter, so their trip from HBM overlaps the tail of the kernel it waits for.  One 128-byte line per
+// lane and step; at most `cols` rows per warp.
+__device__ __forceinline__ void prefetch_weight_rows(const void *W, size_t elem, uint32_t ldw, uint32_t K, uint32_t N, uint32_t warp0, uint32_t nwarps, uint32_t cols) {
+    const uint32_t lane = threadIdx.x & 31u, row_bytes = K * (uint32_t)elem;
+    for (uint32_t n = warp0, c = 0; n < N && c < cols; n += nwarps, c++) {
+        const char *p = static_cast<const char *>(W) + (size_t)n * ldw * elem;
+        for (uint32_t off = lane * 128u; off < row_bytes; off += 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
+    }
 }
 
 __device__ __forceinline__ float gelu_tanh(float z) {
@@ -388,9 +398,19 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     }
 }
 
+// the weight rows this block's warps will read first (plain and fixed-group products; a routed product learns its groups from the
+// kernel before and asks for nothing)
+template <typename WT>
+__device__ __forceinline__ void gemv_prefetch(const GemmArgs &a) {
+    if (a.g_off) return;
+    const WT *W = static_cast<const WT *>(a.W) + (uint64_t)blockIdx.y * a.w_gstride;
+    prefetch_weight_rows(W, sizeof(WT), a.ldw, a.K, a.N, blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), gridDim.x * (blockDim.x >> 5), 2u);
+}
 template <typename WT>
 __global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
-    pdl_enter();
+    pdl_launch_next();
+    gemv_prefetch<WT>(a);
+    pdl_wait();
     __shared__ float red[32];
     gemv_body<WT>(a, red);
 }
@@ -551,7 +571,15 @@ __global__ void __launch_bounds__(1024) k_rglru_scan_par(const ScanArgs a) {
 struct GatesScanArgs { const float *u; const void *W; const float *bias; const float *y; uint32_t ldy; const float *lam; float *S; float *out; uint32_t T, C, bs; float c_decay; uint32_t round_a; };
 template <typename WT>
 __global__ void __launch_bounds__(256) k_rglru_gates_scan(const GatesScanArgs a) {
-    pdl_enter();
+    pdl_launch_next();
+    {   // both gate rows of this warp's channel
+        const uint32_t c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (c < a.C) {
+            prefetch_weight_rows(a.W, sizeof(WT), a.bs, a.bs, a.C, c, a.C, 1u);
+            prefetch_weight_rows(static_cast<const WT *>(a.W) + (size_t)a.C * a.bs, sizeof(WT), a.bs, a.bs, a.C, c, a.C, 1u);
+        }
+    }
+    pdl_wait();
     const uint32_t lane = threadIdx.x & 31u, c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (c >= a.C) return;
     const uint32_t b = c / a.bs, rows = a.T < kGemvMaxM ? a.T : kGemvMaxM;
@@ -616,7 +644,9 @@ __global__ void __launch_bounds__(128) k_latent_norm(const LatentNormArgs a) {
 struct GemvLatentArgs { GemmArgs g; LatentNormArgs n; uint32_t T; };
 template <typename WT>
 __global__ void __launch_bounds__(256) k_gemv_latent(const GemvLatentArgs a) {
-    pdl_enter();
+    pdl_launch_next();
+    gemv_prefetch<WT>(a.g);
+    pdl_wait();
     __shared__ float red[32];
     if (blockIdx.x == gridDim.x - 1u && blockIdx.y == 0)
         for (uint32_t t = 0; t < a.T; t++) latent_kv_row(a.n, t, red);
