@@ -72,7 +72,10 @@ def whole(eng, t, want=None):
                                         # latent ranks of 64 / 128 / 256 take the attention kernel's compile-time-rank instances
                                         ("latent_attention", {"heads": 4, "dim": 8, "vdim": 12, "kv_rank": 64, "q_rank": 24, "scale": 0.4}),
                                         ("latent_attention", {"heads": 9, "dim": 12, "vdim": 8, "kv_rank": 128, "q_rank": 20, "scale": 0.3}),
-                                        ("latent_attention", {"heads": 2, "dim": 8, "vdim": 8, "kv_rank": 256, "q_rank": 16, "scale": 0.2})])
+                                        ("latent_attention", {"heads": 2, "dim": 8, "vdim": 8, "kv_rank": 256, "q_rank": 16, "scale": 0.2}),
+                                        # the widest register tile: a general rank above 256 and the constant 512
+                                        ("latent_attention", {"heads": 3, "dim": 8, "vdim": 8, "kv_rank": 330, "q_rank": 16, "scale": 0.2}),
+                                        ("latent_attention", {"heads": 2, "dim": 8, "vdim": 8, "kv_rank": 512, "q_rank": 16, "scale": 0.15})])
 def test_mixer_alone(tmp_path, kind, mixer):
     cfg = md.famudra_config(61, 72, [(kind, mixer, None)])
     eng, w = build(tmp_path, cfg, keep=True)
