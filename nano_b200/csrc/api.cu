@@ -39,6 +39,7 @@ typedef int (*DirCreate)(nb200_engine **, const nb::ModelDir *, uint32_t, int, u
 struct DirFamily { const char *architecture; DirCreate create; const char *unit; };
 const DirFamily kDirFamilies[] = {
     {"Famudra", nb_family_layered_create, "layered.cu"},
+    {"Rakarax", nb_family_layered_create, "layered.cu"},
 };
 }  // namespace
 

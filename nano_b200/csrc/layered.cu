@@ -1,7 +1,13 @@
 // layered.cu -- the layered model family of libnano_b200.so: decoders described by config.json as a list of typed layers
 // (a token mixer + an optional feed-forward each, over an fp32 residual stream), loaded from model.safetensors.
 //
-// Registered design: "Famudra" -- parallel layers  x <- x + (mixer(shift(norm1 x)) + ff(norm2 x))  with scalar-gain RMS norms and a
+// Registered designs (config.json "architecture"):
+// "Rakarax" -- sequential sublayers with a norm before and after each one, x <- x + norm1b(mixer(norm1 x)), then
+// x <- x + norm2b(ff(norm2 x)), vector-gain RMS norms stored around zero, a learned position row added to the embedding; mixers
+// "retention" (rotary linear attention with a fixed decay per head, fp32 state) and "parallel" (a sliding-window grouped-query
+// attention whose scores are mixed across heads, side by side with a Mamba selective scan, summed with fixed scales); feed-forward
+// "dense" (PolyNorm activation); a layer may use another layer's weights ("weights_of") with cache and state of its own.
+// "Famudra" -- parallel layers  x <- x + (mixer(shift(norm1 x)) + ff(norm2 x))  with scalar-gain RMS norms and a
 // token shift on the mixer input; mixers "rglru" (gelu branch x conv + real-gated linear recurrent unit) and "latent_attention"
 // (queries and keys/values through normed low-rank latents, no positions, causal softmax); feed-forward "moe" (top-k routed
 // squared-relu experts + a shared expert); a span of layers may run several times with the same weights ("loop"), each pass with
@@ -20,6 +26,7 @@
 //                  the chosen token back on the device
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -30,6 +37,7 @@
 
 #include "family.h"
 #include "layered_kernels.cuh"
+#include "layered_mixers.cuh"
 #include "modeldir.h"
 #include "sample_host.h"
 
@@ -42,7 +50,11 @@ namespace {
 
 struct Weight { void *p = nullptr; uint32_t rows = 0, cols = 0; };
 
-enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1 };
+enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1, MIX_RETENTION = 2, MIX_WINDOW_SSM = 3 };
+// how a layer combines its sublayers: Famudra's parallel form with a token shift and scalar-gain norms, or sequential sublayers
+// between an input norm and an output norm each (vector gains stored around zero)
+enum LayerForm { FORM_PARALLEL_SHIFT = 0, FORM_SANDWICH = 1 };
+enum FfKind { FF_NONE = 0, FF_MOE = 1, FF_DENSE_POLY = 2 };
 
 struct Layer {
     int type = 0;
@@ -55,20 +67,33 @@ struct Layer {
     uint32_t H = 0, dim = 0, vdim = 0, R = 0, QR = 0; float scale = 0.0f;
     Weight dqkv, uq, ukT, uv;
     float *dq_norm = nullptr, *dkv_norm = nullptr;
+    // sandwich form: input / output norms of the mixer and of the feed-forward
+    float *n1 = nullptr, *n1b = nullptr, *n2 = nullptr, *n2b = nullptr;
+    // retention: proj = [q | k | v | g]
+    float *decay = nullptr; uint32_t rot_dims = 0; float2 *rot_tab = nullptr;
+    Weight proj;
+    // window attention + selective scan side by side: proj = [q | k | x | g | z]; H, dim as above, G key/value heads
+    uint32_t G = 0, a_taps = 0, window = 0, RL = 0; float softcap = 0.0f, left_scale = 1.0f, right_scale = 1.0f;
+    float *a_conv = nullptr, *temp = nullptr, *talk = nullptr, *slopes = nullptr;
+    uint32_t mC = 0, mN = 0, mR = 0, m_taps = 0;
+    float *m_conv = nullptr, *m_conv_b = nullptr, *dt_b = nullptr, *A = nullptr, *Dv = nullptr;
+    Weight xw, dtw, mo;
     // feed-forward
+    int ff_kind = FF_NONE; float *act = nullptr;
     bool has_mlp = false, has_shared = false;
     uint32_t NE = 0, top = 0, ff = 0, sff = 0;
     float *router = nullptr;
     Weight up, down, sup, sdown;
 };
 
-struct Run { uint32_t layer = 0; bool add_embed = false; size_t st_prev = 0, st_S = 0, st_conv = 0; float *cache = nullptr; };
+struct Run { uint32_t layer = 0; bool add_embed = false; size_t st_prev = 0, st_S = 0, st_conv = 0, st_conv2 = 0; float *cache = nullptr; };
 
 struct Seq { bool live = false; uint32_t len = 0; std::vector<uint32_t> pages; };
 
 constexpr float kRglruDecay = 8.0f;      // a = exp(-8 r softplus(lam)): fixed by the design
 constexpr uint32_t kWantBatch = 64;      // rows of logits computed per head product
 constexpr uint32_t kSplitMax = 32;
+constexpr uint32_t kNoWindow = 1u << 30;      // window of an attention without a mask: every earlier key is seen
 
 }  // namespace
 
@@ -80,7 +105,8 @@ struct LayeredEngine : nb::EngineBase {
     uint32_t V = 0, E = 0; float eps = 0.0f;
     std::vector<Layer> layers; std::vector<Run> runs;
     bool keep_x0 = false;
-    Weight embed, head; float *final_norm = nullptr;
+    int form = FORM_PARALLEL_SHIFT;
+    Weight embed, head, pos_table; float *final_norm = nullptr; uint32_t max_pos = 0;      // max_pos: rows of the position table (0: the design has none)
     // state manager
     uint32_t max_tokens = 0, max_seqs = 0, n_pages = 0, chunk_cap = 0; size_t slot_floats = 0;
     float *state = nullptr, *state_bak = nullptr; uint32_t *table = nullptr;
@@ -90,6 +116,7 @@ struct LayeredEngine : nb::EngineBase {
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
     float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
+    float *b_p = nullptr, *b_qk = nullptr, *b_xc = nullptr, *b_a = nullptr, *b_ro = nullptr, *b_dbc = nullptr, *b_dt = nullptr, *b_y = nullptr, *b_f = nullptr;   // retention, window attention + selective scan, dense feed-forward
     uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
     float *b_xn = nullptr, *logits = nullptr, *keep = nullptr;
@@ -244,7 +271,7 @@ int load_moe(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint
     if (!u32_of(f->get("router"), "experts", &L->NE) || !u32_of(f->get("router"), "top", &L->top) || !u32_of(f->get("expert"), "ff", &L->ff))
         return fail(NB200_EINVAL, "%s: a moe feed-forward needs router.experts, router.top and expert.ff", p.c_str());
     if (!L->NE || !L->top || L->top > L->NE || !L->ff) return fail(NB200_EINVAL, "%s: experts %u / top %u / ff %u unusable", p.c_str(), L->NE, L->top, L->ff);
-    L->has_mlp = true;
+    L->has_mlp = true; L->ff_kind = FF_MOE;
     int r;
     if ((r = ld.vec(p + "router", {L->NE, E}, &L->router))) return r;
     std::vector<std::string> ups, downs; std::vector<uint64_t> ur, dr;
@@ -256,6 +283,104 @@ int load_moe(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint
         if ((r = ld.stacked({p + "shared.up"}, {L->sff}, E, &L->sup)) || (r = ld.stacked({p + "shared.down"}, {E}, L->sff, &L->sdown))) return r;
     }
     return 0;
+}
+
+// rows [first, first + count) of tensor `name` ([total, cols]) appended to *all
+int append_rows(Loader &ld, const std::string &name, uint64_t total, uint64_t cols, uint64_t first, uint64_t count, std::vector<float> *all) {
+    std::vector<float> h; std::vector<uint64_t> sh; int r;
+    if ((r = ld.host_f32(name, &h, &sh)) || (r = ld.expect(name, sh, {total, cols}))) return r;
+    all->insert(all->end(), h.begin() + first * cols, h.begin() + (first + count) * cols);
+    return 0;
+}
+
+int load_retention(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E, uint32_t max_pos) {
+    const nb::Json *decay = m->get("decay");
+    if (!u32_of(m, "heads", &L->H) || !u32_of(m, "dim", &L->dim) || !u32_of(m, "vdim", &L->vdim) || !decay || decay->t != nb::Json::Arr)
+        return fail(NB200_EINVAL, "%s: a retention mixer needs heads, dim, vdim and the list decay", p.c_str());
+    if (!L->H || !L->dim || !L->vdim || decay->arr.size() != L->H) return fail(NB200_EINVAL, "%s: heads %u / dim %u / vdim %u / %zu decays unusable", p.c_str(), L->H, L->dim, L->vdim, decay->arr.size());
+    if (L->dim > 256) return fail(NB200_EINVAL, "%s: dim %u above 256 has no retention kernel", p.c_str(), L->dim);
+    const uint64_t H = L->H, D = L->dim, VD = L->vdim;
+    std::vector<float> dec(H);
+    for (uint32_t h = 0; h < H; h++) { if (decay->arr[h].t != nb::Json::Num) return fail(NB200_EINVAL, "%s: decay[%u] is no number", p.c_str(), h); dec[h] = (float)decay->arr[h].num; }
+    int r;
+    if ((r = ld.put_f32(dec, &L->decay))) return r;
+    if (m->present("rot")) {
+        const nb::Json *rot = m->get("rot");
+        double base;
+        if (!u32_of(rot, "dims", &L->rot_dims) || !rot->number("base", &base) || L->rot_dims > L->dim || (L->rot_dims & 1u) || !(base > 0.0))
+            return fail(NB200_EINVAL, "%s: rot needs an even dims <= dim and a base > 0", p.c_str());
+        const uint32_t half = L->rot_dims / 2u;
+        if (half) {
+            if (!max_pos) return fail(NB200_EINVAL, "%s: rotary positions need the model's position count", p.c_str());
+            std::vector<float> tab((size_t)max_pos * half * 2);
+            for (uint32_t i = 0; i < half; i++) {
+                const double f = pow(base, -2.0 * (double)i / (double)L->rot_dims);
+                for (uint32_t q = 0; q < max_pos; q++) { const double a = (double)q * f; tab[((size_t)q * half + i) * 2] = (float)cos(a); tab[((size_t)q * half + i) * 2 + 1] = (float)sin(a); }
+            }
+            float *t = nullptr;
+            if ((r = ld.put_f32(tab, &t))) return r;
+            L->rot_tab = reinterpret_cast<float2 *>(t);
+        }
+    }
+    if ((r = ld.stacked({p + "q", p + "k", p + "v", p + "g"}, {H * D, H * D, H * VD, H * VD}, E, &L->proj))) return r;
+    return ld.stacked({p + "o"}, {E}, H * VD, &L->o);
+}
+
+int load_window_ssm(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E) {
+    const nb::Json *lf = m->get("left"), *rt = m->get("right");
+    double ls, rs, sc;
+    if (!lf || lf->t != nb::Json::Obj || !rt || rt->t != nb::Json::Obj || !m->number("left_scale", &ls) || !m->number("right_scale", &rs))
+        return fail(NB200_EINVAL, "%s: a parallel mixer needs left, right, left_scale and right_scale", p.c_str());
+    L->left_scale = (float)ls; L->right_scale = (float)rs;
+    if (!u32_of(lf, "heads", &L->H) || !u32_of(lf, "kv_heads", &L->G) || !u32_of(lf, "dim", &L->dim) || !u32_of(lf, "vdim", &L->vdim) || !u32_of(lf, "conv", &L->a_taps) || !lf->number("scale", &sc))
+        return fail(NB200_EINVAL, "%sleft: window attention needs heads, kv_heads, dim, vdim, conv and scale", p.c_str());
+    L->scale = (float)sc;
+    if (!L->H || !L->G || L->H % L->G || !L->dim || !L->a_taps) return fail(NB200_EINVAL, "%sleft: heads %u / kv_heads %u / dim %u / conv %u unusable", p.c_str(), L->H, L->G, L->dim, L->a_taps);
+    if (L->vdim != L->dim) return fail(NB200_EINVAL, "%sleft: the values are the keys, so vdim %u must equal dim %u", p.c_str(), L->vdim, L->dim);
+    if (L->H > 32 || L->dim > 256) return fail(NB200_EINVAL, "%sleft: more than 32 heads or dim above 256 has no window-attention kernel", p.c_str());
+    L->window = kNoWindow;
+    if (lf->present("mask")) {
+        if (!u32_of(lf->get("mask"), "size", &L->window) || !L->window) return fail(NB200_EINVAL, "%sleft: mask.size must be a positive integer", p.c_str());
+        L->window = std::min(L->window, kNoWindow);
+    }
+    if (lf->present("softcap")) { double c; if (!lf->number("softcap", &c) || !(c >= 0.0)) return fail(NB200_EINVAL, "%sleft: softcap must be a number >= 0", p.c_str()); L->softcap = (float)c; }
+    if (!u32_of(rt, "inner", &L->mC) || !u32_of(rt, "state", &L->mN) || !u32_of(rt, "dt_rank", &L->mR) || !u32_of(rt, "conv", &L->m_taps) || !L->mC || !L->mN || !L->mR || !L->m_taps)
+        return fail(NB200_EINVAL, "%sright: a selective scan needs inner, state, dt_rank and conv", p.c_str());
+    if (L->mN > 128) return fail(NB200_EINVAL, "%sright: state %u above 128 has no scan kernel", p.c_str(), L->mN);
+    const uint64_t H = L->H, G = L->G, D = L->dim, C = L->mC, N = L->mN, R = L->mR;
+    L->RL = (uint32_t)((G * D + G + 3u) & ~(uint64_t)3u);
+    int r;
+    {   // one product for both sides: [q | k | x | g | z]
+        std::vector<float> all;
+        if ((r = append_rows(ld, p + "left.q", H * D, E, 0, H * D, &all)) || (r = append_rows(ld, p + "left.k", G * D, E, 0, G * D, &all)) ||
+            (r = append_rows(ld, p + "right.in", 2 * C, E, 0, C, &all)) || (r = append_rows(ld, p + "left.g", H * D, E, 0, H * D, &all)) ||
+            (r = append_rows(ld, p + "right.in", 2 * C, E, C, C, &all))) return r;
+        if ((r = ld.put_w(all, (uint32_t)(2 * H * D + G * D + 2 * C), E, &L->proj))) return r;
+    }
+    {   // taps of q and of k, one channel range
+        std::vector<float> taps;
+        if ((r = append_rows(ld, p + "left.q.conv", H * D, L->a_taps, 0, H * D, &taps)) || (r = append_rows(ld, p + "left.k.conv", G * D, L->a_taps, 0, G * D, &taps)) ||
+            (r = ld.put_f32(taps, &L->a_conv))) return r;
+    }
+    if ((r = ld.vec(p + "left.temp", {H}, &L->temp)) || (r = ld.vec(p + "left.talk", {H, H}, &L->talk)) || (r = ld.stacked({p + "left.o"}, {E}, H * D, &L->o))) return r;
+    std::vector<float> sl(H);
+    for (uint32_t h = 0; h < H; h++) sl[h] = (float)pow(2.0, -8.0 * (double)(h + 1) / (double)H);
+    if ((r = ld.put_f32(sl, &L->slopes))) return r;
+    if ((r = ld.vec(p + "right.conv", {C, L->m_taps}, &L->m_conv)) || (r = ld.vec(p + "right.conv.b", {C}, &L->m_conv_b)) || (r = ld.vec(p + "right.dt.b", {C}, &L->dt_b)) ||
+        (r = ld.vec(p + "right.D", {C}, &L->Dv)) || (r = ld.stacked({p + "right.x"}, {R + 2 * N}, C, &L->xw)) || (r = ld.stacked({p + "right.dt"}, {C}, R, &L->dtw)) ||
+        (r = ld.stacked({p + "right.o"}, {E}, C, &L->mo))) return r;
+    std::vector<float> al; std::vector<uint64_t> sh;
+    if ((r = ld.host_f32(p + "right.A_log", &al, &sh)) || (r = ld.expect(p + "right.A_log", sh, {C, N}))) return r;
+    for (float &v : al) v = (float)-exp((double)v);          // A = -exp(A_log)
+    return ld.put_f32(al, &L->A);
+}
+
+int load_dense(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(f, "ff", &L->ff) || !L->ff) return fail(NB200_EINVAL, "%s: a dense feed-forward needs ff", p.c_str());
+    L->has_mlp = true; L->ff_kind = FF_DENSE_POLY;
+    int r;
+    if ((r = ld.stacked({p + "up"}, {L->ff}, E, &L->up)) || (r = ld.stacked({p + "down"}, {E}, L->ff, &L->down))) return r;
+    return ld.vec(p + "act", {4}, &L->act);
 }
 
 // ---------------- launches ----------------
@@ -334,78 +459,226 @@ int attn_optin(int smem) {
     return 0;
 }
 
+// ---------------- mixers: e->hm [T][E] -> e->d [T][E], from the cache pages and the state slot of the sequence ----------------
+struct Ctx { float *st; const uint32_t *table; uint32_t T, pos0; const uint32_t *pos_ptr; };
+
+int mix_rglru(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T; float *st = cx.st; int r;
+    const uint32_t C = L.C, bs = C / L.blocks;
+    if (T <= kGemvMaxM) {
+        // short portions: the convolution is the epilogue of the [y | x] product, gates and recurrence are one kernel
+        GemmArgs yx = plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_CONV, C);
+        yx.cv_taps = L.conv; yx.cv_bias = L.conv_b; yx.cv_state = st + run.st_conv; yx.cv_out = e->b_u; yx.cv_K = L.taps;
+        if ((r = gemm(e, yx, 1, T))) return r;
+        GatesScanArgs gs{e->b_u, L.gates.p, L.gates_b, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, bs, kRglruDecay, e->f32 ? 0u : 1u};
+        const dim3 grid((C + 7u) / 8u), block(256);
+        if ((r = e->f32 ? launch<GatesScanArgs>(e, k_rglru_gates_scan<float>, grid, block, 0, gs) : launch<GatesScanArgs>(e, k_rglru_gates_scan<__nv_bfloat16>, grid, block, 0, gs))) return r;
+    } else {
+        if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
+        ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
+        if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
+        if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
+        GemmArgs g{};
+        g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
+        g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
+        if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
+        ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
+        if (T <= 32) { if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r; }
+        else if ((r = launch<ScanArgs>(e, k_rglru_scan_par, dim3((C + 31) / 32), dim3(32, T >= 256 ? 32 : 8), 0, sa))) return r;
+    }
+    if ((r = gemm(e, plain(e->b_sy, C, L.o, e->d, E, T), 1, T))) return r;
+    return 0;
+}
+
+int mix_latent_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T, pos0 = cx.pos0; const uint32_t *table = cx.table, *pos_ptr = cx.pos_ptr; int r;
+    const uint32_t H = L.H, R = L.R, QR = L.QR;
+    if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
+    LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
+    if (T <= kGemvMaxM) {      // the norms ride on the query up-projection
+        GemvLatentArgs ga{plain(e->b_z, QR + R, L.uq, e->b_q, H * L.dim, T), na, T};
+        ga.g.a_norm_w = L.dq_norm; ga.g.a_eps = e->eps; ga.g.round_a = e->f32 ? 0u : 1u;
+        const dim3 grid(gemv_blocks(e, ga.g.N, 1)), block(256);
+        if ((r = e->f32 ? launch<GemvLatentArgs>(e, k_gemv_latent<float>, grid, block, 0, ga) : launch<GemvLatentArgs>(e, k_gemv_latent<__nv_bfloat16>, grid, block, 0, ga))) return r;
+    } else {
+        if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
+        if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+    }
+    GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
+    g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
+    g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
+    if ((r = gemm(e, g, H, T))) return r;
+    AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr, e->b_tick};
+    if (pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
+    else if (T <= kGemvMaxM) {
+        const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
+        aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
+    }
+    if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
+    GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
+    v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
+    v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
+    if ((r = gemm(e, v, H, T))) return r;
+    if ((r = gemm(e, plain(e->b_ov, H * L.vdim, L.o, e->d, E, T), 1, T))) return r;
+    return 0;
+}
+
+// retention: [q | k | v | g] in one product, rotary positions on q and k (k scaled by dim^-1/2 afterwards), the recurrence over the
+// fp32 state of the slot, per-head unit RMS times silu(g), output product
+int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T, H = L.H, D = L.dim, VD = L.vdim, P = 2 * H * D + 2 * H * VD;
+    int r;
+    if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T), 1, T))) return r;
+    RopeArgs ra{e->b_p, P, 0, H * D, T, H, D, L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr};
+    if ((r = launch<RopeArgs>(e, k_rope, dim3(ew_grid((size_t)T * H * (D - L.rot_dims / 2u))), dim3(256), 0, ra))) return r;
+    RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD};
+    const dim3 grid((H * VD + 7u) / 8u), block(256);
+    if (D <= 32) r = launch<RetentionArgs>(e, k_retention_scan<1>, grid, block, 0, sa);
+    else if (D <= 64) r = launch<RetentionArgs>(e, k_retention_scan<2>, grid, block, 0, sa);
+    else if (D <= 128) r = launch<RetentionArgs>(e, k_retention_scan<4>, grid, block, 0, sa);
+    else r = launch<RetentionArgs>(e, k_retention_scan<8>, grid, block, 0, sa);
+    if (r) return r;
+    RetOutArgs oa{e->b_ro, e->b_p + 2 * H * D + H * VD, P, e->b_a, T, H, VD, e->eps};
+    if ((r = launch<RetOutArgs>(e, k_retention_out, dim3((T * H + 7u) / 8u), dim3(256), 0, oa))) return r;
+    return gemm(e, plain(e->b_a, H * VD, L.o, e->d, E, T), 1, T);
+}
+
+template <int VCH>
+int win_attn_launch_v(LayeredEngine *e, const WinAttnArgs &a, uint32_t qt, uint32_t hs) {
+    const uint32_t warps = (a.H + hs - 1) / hs;
+    const dim3 grid((a.T + qt - 1) / qt), block(warps * 32);
+    const size_t smem = win_attn_smem(a.H, a.D, a.RL, qt);
+    if (hs == 1) {
+        if (qt == 8) return launch<WinAttnArgs>(e, k_window_attn<VCH, 8, 1>, grid, block, smem, a);
+        if (qt == 4) return launch<WinAttnArgs>(e, k_window_attn<VCH, 4, 1>, grid, block, smem, a);
+        return launch<WinAttnArgs>(e, k_window_attn<VCH, 1, 1>, grid, block, smem, a);
+    }
+    if (qt == 4) return launch<WinAttnArgs>(e, k_window_attn<VCH, 4, 2>, grid, block, smem, a);
+    return launch<WinAttnArgs>(e, k_window_attn<VCH, 1, 2>, grid, block, smem, a);
+}
+template <int VCH>
+int win_attn_optin_v(int smem) {
+    CK(cudaFuncSetAttribute((const void *)k_window_attn<VCH, 8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_window_attn<VCH, 4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_window_attn<VCH, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_window_attn<VCH, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_window_attn<VCH, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    return 0;
+}
+constexpr size_t kWinSmemMax = 200 * 1024;
+// query tokens per block of a prefill portion: the largest of 8 / 4 / 1 whose shared memory fits (heads above 16: two per warp, 4 at most)
+uint32_t win_attn_qt(const Layer &L) {
+    const uint32_t hs = L.H > 16 ? 2u : 1u;
+    for (uint32_t qt : {8u, 4u, 1u}) if (!(hs == 2 && qt == 8) && win_attn_smem(L.H, L.dim, L.RL, qt) <= kWinSmemMax) return qt;
+    return 0;
+}
+int win_attn_launch(LayeredEngine *e, const Layer &L, const WinAttnArgs &a) {
+    const uint32_t hs = L.H > 16 ? 2u : 1u, qt = a.T <= kGemvMaxM ? 1u : win_attn_qt(L);
+    if (L.dim <= 32) return win_attn_launch_v<1>(e, a, qt, hs);
+    if (L.dim <= 64) return win_attn_launch_v<2>(e, a, qt, hs);
+    if (L.dim <= 128) return win_attn_launch_v<4>(e, a, qt, hs);
+    return win_attn_launch_v<8>(e, a, qt, hs);
+}
+
+template <int LG>
+int sel_scan_launch(LayeredEngine *e, const SelScanArgs &a) {
+    return launch<SelScanArgs>(e, k_selective_scan<LG>, dim3(((size_t)a.C * LG + 255u) / 256u), dim3(256), 0, a);
+}
+
+int conv_launch(LayeredEngine *e, const ConvArgs &ca) {
+    int r;
+    if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)ca.T * ca.C)), dim3(256), 0, ca))) return r;
+    if (ca.K > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((ca.C + 127) / 128), dim3(128), 0, ca))) return r;
+    return 0;
+}
+
+// window attention and selective scan on the same input: one product gives [q | k | x | g | z]; q, k pass their convolution (tail in
+// the slot), the convolved k is cached as value and key; x passes its convolution with bias and silu, gives [dt | B | C], dt its
+// softplus; the two output products are summed with the layer's scales
+int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T, H = L.H, G = L.G, D = L.dim, C = L.mC, N = L.mN, R = L.mR;
+    const uint32_t QK = H * D + G * D, P = QK + C + H * D + C, g0 = QK + C, z0 = g0 + H * D;
+    int r;
+    if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T), 1, T))) return r;
+    if ((r = conv_launch(e, ConvArgs{e->b_p, P, L.a_conv, nullptr, cx.st + run.st_conv, e->b_qk, T, QK, L.a_taps, QK, 0}))) return r;
+    if ((r = conv_launch(e, ConvArgs{e->b_p + QK, P, L.m_conv, L.m_conv_b, cx.st + run.st_conv2, e->b_xc, T, C, L.m_taps, C, 1}))) return r;
+    // left
+    QkPrepArgs qa{e->b_qk, QK, e->b_qk + H * D, QK, L.temp, L.scale, run.cache, cx.table, H, G, D, L.RL, cx.pos0, e->eps, cx.pos_ptr};
+    if ((r = launch<QkPrepArgs>(e, k_qk_prepare, dim3(T), dim3(256), 0, qa))) return r;
+    WinAttnArgs wa{e->b_qk, QK, run.cache, cx.table, e->b_p + g0, P, L.talk, L.slopes, e->b_a, T, H, G, D, L.RL, cx.pos0, L.window, L.softcap, cx.pos_ptr};
+    if ((r = win_attn_launch(e, L, wa))) return r;
+    // right
+    if ((r = gemm(e, plain(e->b_xc, C, L.xw, e->b_dbc, R + 2 * N, T), 1, T))) return r;
+    if ((r = gemm(e, plain(e->b_dbc, R + 2 * N, L.dtw, e->b_dt, C, T, L.dt_b, EPI_SOFTPLUS), 1, T))) return r;
+    SelScanArgs sa{e->b_dt, e->b_xc, e->b_dbc, R + 2 * N, R, R + N, L.A, L.Dv, e->b_p + z0, P, cx.st + run.st_S, e->b_y, T, C, N};
+    if (N <= 4) r = sel_scan_launch<1>(e, sa);
+    else if (N <= 8) r = sel_scan_launch<2>(e, sa);
+    else if (N <= 16) r = sel_scan_launch<4>(e, sa);
+    else if (N <= 32) r = sel_scan_launch<8>(e, sa);
+    else if (N <= 64) r = sel_scan_launch<16>(e, sa);
+    else r = sel_scan_launch<32>(e, sa);
+    if (r) return r;
+    GemmArgs lo = plain(e->b_a, H * D, L.o, e->d, E, T), ro = plain(e->b_y, C, L.mo, e->d, E, T);
+    lo.c_scale = L.left_scale; lo.c_mode = C_SCALE; ro.c_scale = L.right_scale; ro.c_mode = C_SCALE | C_ADD;
+    if ((r = gemm(e, lo, 1, T))) return r;
+    return gemm(e, ro, 1, T);
+}
+
+int mix(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    switch (L.type) {
+        case MIX_RGLRU: return mix_rglru(e, L, run, cx);
+        case MIX_LATENT_ATTN: return mix_latent_attn(e, L, run, cx);
+        case MIX_RETENTION: return mix_retention(e, L, run, cx);
+        default: return mix_window_ssm(e, L, run, cx);
+    }
+}
+
+// dense feed-forward with the PolyNorm activation: e->h2 -> e->d
+int ff_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
+    int r;
+    if ((r = gemm(e, plain(e->h2, e->E, L.up, e->b_f, L.ff, T), 1, T))) return r;
+    PolyArgs pa{e->b_f, L.ff, L.act, T, L.ff, e->eps};
+    if ((r = launch<PolyArgs>(e, k_polynorm, dim3(T), dim3(256), 0, pa))) return r;
+    return gemm(e, plain(e->b_f, L.ff, L.down, e->d, e->E, T), 1, T);
+}
+
+int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T) {
+    SandwichArgs a{e->x, d, w_post, w_pre, out, keep, T, e->E, e->eps};
+    return launch<SandwichArgs>(e, k_sandwich, dim3(T), dim3(256), 0, a);
+}
+
 // every layer run over T tokens (x already holds their embeddings) of the sequence in `slot`, whose first token sits at pos0
 // (+ *pos_ptr: a captured decode step keeps the position on the device and uses a fixed number of key splits)
 int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const uint32_t *pos_ptr = nullptr) {
     const uint32_t E = e->E;
     float *st = e->state + (size_t)slot * e->slot_floats;
-    const uint32_t *table = e->table + (size_t)slot * e->n_pages;
+    const Ctx cx{st, e->table + (size_t)slot * e->n_pages, T, pos0, pos_ptr};
     int r;
     e->cur = e->stream;
     for (size_t ri = 0; ri < e->runs.size(); ri++) {
         const Run &run = e->runs[ri];
         const Layer &L = e->layers[run.layer];
+        float *keep = e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr;
+        if (e->form == FORM_SANDWICH) {
+            // x <- x + norm1b(mixer(norm1 x)), x <- x + norm2b(ff(norm2 x)): each residual update also norms the updated x for the
+            // sublayer that follows (this layer's feed-forward, or the next run's mixer)
+            const float *next_n1 = ri + 1 < e->runs.size() ? e->layers[e->runs[ri + 1].layer].n1 : nullptr;
+            if (ri == 0 && (r = sandwich(e, nullptr, nullptr, L.n1, e->hm, nullptr, T))) return r;
+            if ((r = mix(e, L, run, cx))) return r;
+            if (L.has_mlp) {
+                if ((r = sandwich(e, e->d, L.n1b, L.n2, e->h2, nullptr, T)) || (r = ff_dense(e, L, T)) ||
+                    (r = sandwich(e, e->d, L.n2b, next_n1, next_n1 ? e->hm : nullptr, keep, T))) return r;
+            } else if ((r = sandwich(e, e->d, L.n1b, next_n1, next_n1 ? e->hm : nullptr, keep, T))) return r;
+            continue;
+        }
         if (run.add_embed) { k_add<<<ew_grid((size_t)T * E), 256, 0, e->stream>>>(e->x, e->x0, (size_t)T * E); CK(cudaGetLastError()); e->launches++; }
         {
             NormShiftArgs a{e->x, L.norm1, L.has_mlp ? L.norm2 : nullptr, L.shift, st + run.st_prev, e->hm, L.has_mlp ? e->h2 : nullptr, T, E, e->eps};
             if ((r = launch<NormShiftArgs>(e, k_norm_shift, dim3(T > 1 ? T - 1 : 1), dim3(256), 0, a))) return r;
             if (L.has_mlp && e->branch_streams) CK(cudaEventRecord(e->ev_fork, e->stream));
         }
-        if (L.type == MIX_RGLRU) {
-            const uint32_t C = L.C, bs = C / L.blocks;
-            if (T <= kGemvMaxM) {
-                // short portions: the convolution is the epilogue of the [y | x] product, gates and recurrence are one kernel
-                GemmArgs yx = plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_CONV, C);
-                yx.cv_taps = L.conv; yx.cv_bias = L.conv_b; yx.cv_state = st + run.st_conv; yx.cv_out = e->b_u; yx.cv_K = L.taps;
-                if ((r = gemm(e, yx, 1, T))) return r;
-                GatesScanArgs gs{e->b_u, L.gates.p, L.gates_b, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, bs, kRglruDecay, e->f32 ? 0u : 1u};
-                const dim3 grid((C + 7u) / 8u), block(256);
-                if ((r = e->f32 ? launch<GatesScanArgs>(e, k_rglru_gates_scan<float>, grid, block, 0, gs) : launch<GatesScanArgs>(e, k_rglru_gates_scan<__nv_bfloat16>, grid, block, 0, gs))) return r;
-            } else {
-                if ((r = gemm(e, plain(e->hm, E, L.yx, e->b_yx, 2 * C, T, L.yx_b, EPI_GELU_SPLIT, C), 1, T))) return r;
-                ConvArgs ca{e->b_yx + C, 2 * C, L.conv, L.conv_b, st + run.st_conv, e->b_u, T, C, L.taps};
-                if ((r = launch<ConvArgs>(e, k_conv, dim3(ew_grid((size_t)T * C)), dim3(256), 0, ca))) return r;
-                if (L.taps > 1 && (r = launch<ConvArgs>(e, k_conv_state, dim3((C + 127) / 128), dim3(128), 0, ca))) return r;
-                GemmArgs g{};
-                g.A = e->b_u; g.lda = C; g.W = L.gates.p; g.ldw = bs; g.C = e->b_g; g.ldc = 2 * C; g.bias = L.gates_b; g.M = T; g.N = bs; g.K = bs;
-                g.a_gmod = L.blocks; g.a_gcols = bs; g.c_gcols = bs; g.b_gstride = bs; g.w_gstride = (uint64_t)bs * bs; g.epi = EPI_SIGMOID;
-                if ((r = gemm(e, g, 2 * L.blocks, T))) return r;
-                ScanArgs sa{e->b_g, 2 * C, e->b_u, e->b_yx, 2 * C, L.lam, st + run.st_S, e->b_sy, T, C, kRglruDecay};
-                if (T <= 32) { if ((r = launch<ScanArgs>(e, k_rglru_scan, dim3((C + 63) / 64), dim3(64), 0, sa))) return r; }
-                else if ((r = launch<ScanArgs>(e, k_rglru_scan_par, dim3((C + 31) / 32), dim3(32, T >= 256 ? 32 : 8), 0, sa))) return r;
-            }
-            if ((r = gemm(e, plain(e->b_sy, C, L.o, e->d, E, T), 1, T))) return r;
-        } else {
-            const uint32_t H = L.H, R = L.R, QR = L.QR;
-            if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
-            LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
-            if (T <= kGemvMaxM) {      // the norms ride on the query up-projection
-                GemvLatentArgs ga{plain(e->b_z, QR + R, L.uq, e->b_q, H * L.dim, T), na, T};
-                ga.g.a_norm_w = L.dq_norm; ga.g.a_eps = e->eps; ga.g.round_a = e->f32 ? 0u : 1u;
-                const dim3 grid(gemv_blocks(e, ga.g.N, 1)), block(256);
-                if ((r = e->f32 ? launch<GemvLatentArgs>(e, k_gemv_latent<float>, grid, block, 0, ga) : launch<GemvLatentArgs>(e, k_gemv_latent<__nv_bfloat16>, grid, block, 0, ga))) return r;
-            } else {
-                if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
-                if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
-            }
-            GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
-            g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
-            g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
-            if ((r = gemm(e, g, H, T))) return r;
-            AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr, e->b_tick};
-            if (pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
-            else if (T <= kGemvMaxM) {
-                const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
-                aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
-            }
-            if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
-            GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
-            v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
-            v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
-            if ((r = gemm(e, v, H, T))) return r;
-            if ((r = gemm(e, plain(e->b_ov, H * L.vdim, L.o, e->d, E, T), 1, T))) return r;
-        }
-        CombineArgs c{e->x, e->d, nullptr, nullptr, nullptr, nullptr, e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr, T, E, 0};
+        if ((r = mix(e, L, run, cx))) return r;
+        CombineArgs c{e->x, e->d, nullptr, nullptr, nullptr, nullptr, keep, T, E, 0};
         if (L.has_mlp) {
             // The layer is parallel: the feed-forward reads h2 = norm2(x) of the SAME x and shares no buffer with the mixer, so its
             // kernels go to a second stream (a parallel branch of the captured decode graph) and join before the residual update.
@@ -437,7 +710,14 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
     return 0;
 }
 
-int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr) {
+int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr, uint32_t pos0 = 0) {
+    if (e->max_pos) {      // a learned position row joins the token row
+        if (e->f32) k_embed_pos<float><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const float *)e->embed.p, (const float *)e->pos_table.p, e->x, e->E, pos0);
+        else k_embed_pos<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const __nv_bfloat16 *)e->embed.p, (const __nv_bfloat16 *)e->pos_table.p, e->x, e->E, pos0);
+        CK(cudaGetLastError());
+        e->launches++;
+        return 0;
+    }
     if (e->f32) k_embed<float><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const float *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
     else k_embed<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const __nv_bfloat16 *)e->embed.p, e->x, e->keep_x0 ? e->x0 : nullptr, e->E);
     CK(cudaGetLastError());
@@ -447,7 +727,7 @@ int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const ui
 
 // logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
 int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr) {
-    k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
+    k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps, e->form == FORM_SANDWICH ? 1u : 0u);
     CK(cudaGetLastError());
     e->launches++;
     return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);
@@ -493,6 +773,7 @@ int seq_check(LayeredEngine *e, uint32_t seq) {
 int reserve_pages(LayeredEngine *e, uint32_t seq, uint32_t tokens) {
     Seq &s = e->seqs[seq];
     const size_t have = s.pages.size(), need = (tokens + kPage - 1) / kPage;
+    if (e->max_pos && tokens > e->max_pos) return fail(NB200_EINVAL, "sequence %u would reach %u tokens; the model has %u positions", seq, tokens, e->max_pos);
     if (need <= have) return 0;
     if (need - have > e->free_pages.size()) return fail(NB200_ENOMEM, "the cache is full: %u tokens asked for sequence %u, %zu pages free", tokens, seq, e->free_pages.size());
     for (size_t i = have; i < need; i++) { s.pages.push_back(e->free_pages.back()); e->free_pages.pop_back(); }
@@ -535,7 +816,7 @@ int step_dev(LayeredEngine *e, uint32_t seq, const uint32_t *tok_dev, uint32_t n
     uint32_t wi = 0;
     for (uint32_t c0 = 0; c0 < n; c0 += e->chunk_cap) {
         const uint32_t T = std::min(e->chunk_cap, n - c0);
-        if ((r = embed_tokens(e, tok_dev + c0, T)) || (r = run_layers(e, seq, T, s.len))) return r;
+        if ((r = embed_tokens(e, tok_dev + c0, T, nullptr, s.len)) || (r = run_layers(e, seq, T, s.len))) return r;
         s.len += T;
         while (wi < n_want && want[wi] < c0 + T) {
             uint32_t idx[kWantBatch], nw = 0;
@@ -835,32 +1116,68 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     const uint32_t E = e->E, NL = (uint32_t)layers->arr.size();
     Loader ld{e, dir};
     int r;
-    if ((r = ld.stacked({"embed"}, {e->V}, E, &e->embed)) || (r = ld.stacked({"head"}, {e->V}, E, &e->head)) || (r = ld.vec("final.norm", {}, &e->final_norm))) return r;
+    const nb::Json *arch = cfg.get("architecture");
+    e->form = arch && arch->t == nb::Json::Str && arch->str == "Rakarax" ? FORM_SANDWICH : FORM_PARALLEL_SHIFT;
+    if ((r = ld.stacked({"embed"}, {e->V}, E, &e->embed)) || (r = ld.stacked({"head"}, {e->V}, E, &e->head))) return r;
     e->layers.resize(NL);
-    for (uint32_t i = 0; i < NL; i++) {
-        const nb::Json &lj = layers->arr[i];
-        Layer &L = e->layers[i];
-        const std::string p = "l" + std::to_string(i) + ".";
-        const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
-        if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
-        if ((r = ld.vec(p + "norm1", {}, &L.norm1)) || (r = ld.vec(p + "shift", {E}, &L.shift))) return r;
-        if (type->str == "rglru") { L.type = MIX_RGLRU; r = load_rglru(ld, mixer, p + "mix.", &L, E); }
-        else if (type->str == "latent_attention") { L.type = MIX_LATENT_ATTN; r = load_latent_attn(ld, mixer, p + "mix.", &L, E); }
-        else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
-        if (r) return r;
-        if (lj.present("mlp")) {
-            if ((r = ld.vec(p + "norm2", {}, &L.norm2)) || (r = load_moe(ld, lj.get("mlp"), p + "mlp.", &L, E))) return r;
+    if (e->form == FORM_SANDWICH) {
+        auto pt = dir->tensors.find("pos");
+        if (pt == dir->tensors.end() || pt->second.shape.size() != 2 || pt->second.shape[0] == 0) return fail(NB200_EINVAL, "model.safetensors has no position table \"pos\" [positions, width]");
+        e->max_pos = (uint32_t)pt->second.shape[0];
+        if ((r = ld.stacked({"pos"}, {e->max_pos}, E, &e->pos_table)) || (r = ld.vec("final.norm", {E}, &e->final_norm))) return r;
+        // a layer with "weights_of": j runs layer j's tensors with cache and state of its own
+        std::vector<uint32_t> owner(NL);
+        for (uint32_t i = 0; i < NL; i++) {
+            owner[i] = i;
+            if (layers->arr[i].present("weights_of") && (!u32_of(&layers->arr[i], "weights_of", &owner[i]) || owner[i] >= NL || layers->arr[owner[i]].present("weights_of")))
+                return fail(NB200_EINVAL, "layer %u: weights_of must name a layer with weights of its own", i);
         }
+        for (uint32_t i = 0; i < NL; i++) {
+            Run q; q.layer = owner[i]; e->runs.push_back(q);
+            if (owner[i] != i) continue;
+            const nb::Json &lj = layers->arr[i];
+            Layer &L = e->layers[i];
+            const std::string p = "l" + std::to_string(i) + ".";
+            const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
+            if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
+            if ((r = ld.vec(p + "norm1", {E}, &L.n1)) || (r = ld.vec(p + "norm1b", {E}, &L.n1b))) return r;
+            if (type->str == "retention") { L.type = MIX_RETENTION; r = load_retention(ld, mixer, p + "mix.", &L, E, e->max_pos); }
+            else if (type->str == "parallel") { L.type = MIX_WINDOW_SSM; r = load_window_ssm(ld, mixer, p + "mix.", &L, E); }
+            else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
+            if (r) return r;
+            if (lj.present("mlp")) {
+                const nb::Json *f = lj.get("mlp"), *kind = f->get("kind");
+                if (!kind || kind->t != nb::Json::Str || kind->str != "dense") return fail(NB200_EINVAL, "layer %u: feed-forward kind \"%s\" is not known here", i, kind && kind->t == nb::Json::Str ? kind->str.c_str() : "?");
+                if ((r = ld.vec(p + "norm2", {E}, &L.n2)) || (r = ld.vec(p + "norm2b", {E}, &L.n2b)) || (r = load_dense(ld, f, p + "mlp.", &L, E))) return r;
+            }
+        }
+    } else {
+        if ((r = ld.vec("final.norm", {}, &e->final_norm))) return r;
+        for (uint32_t i = 0; i < NL; i++) {
+            const nb::Json &lj = layers->arr[i];
+            Layer &L = e->layers[i];
+            const std::string p = "l" + std::to_string(i) + ".";
+            const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
+            if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
+            if ((r = ld.vec(p + "norm1", {}, &L.norm1)) || (r = ld.vec(p + "shift", {E}, &L.shift))) return r;
+            if (type->str == "rglru") { L.type = MIX_RGLRU; r = load_rglru(ld, mixer, p + "mix.", &L, E); }
+            else if (type->str == "latent_attention") { L.type = MIX_LATENT_ATTN; r = load_latent_attn(ld, mixer, p + "mix.", &L, E); }
+            else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
+            if (r) return r;
+            if (lj.present("mlp")) {
+                if ((r = ld.vec(p + "norm2", {}, &L.norm2)) || (r = load_moe(ld, lj.get("mlp"), p + "mlp.", &L, E))) return r;
+            }
+        }
+        // order of the layer runs
+        uint32_t lo = 0, hi = 0, times = 1;
+        if (cfg.present("loop")) {
+            const nb::Json *lp = cfg.get("loop");
+            if (!u32_of(lp, "start", &lo) || !u32_of(lp, "stop", &hi) || !u32_of(lp, "times", &times) || lo > hi || hi > NL || times < 1) return fail(NB200_EINVAL, "loop needs 0 <= start <= stop <= layers and times >= 1");
+        }
+        for (uint32_t i = 0; i < lo; i++) { Run q; q.layer = i; e->runs.push_back(q); }
+        for (uint32_t p = 0; p < times; p++) for (uint32_t i = lo; i < hi; i++) { Run q; q.layer = i; q.add_embed = p > 0 && i == lo; e->runs.push_back(q); if (q.add_embed) e->keep_x0 = true; }
+        for (uint32_t i = hi; i < NL; i++) { Run q; q.layer = i; e->runs.push_back(q); }
     }
-    // order of the layer runs
-    uint32_t lo = 0, hi = 0, times = 1;
-    if (cfg.present("loop")) {
-        const nb::Json *lp = cfg.get("loop");
-        if (!u32_of(lp, "start", &lo) || !u32_of(lp, "stop", &hi) || !u32_of(lp, "times", &times) || lo > hi || hi > NL || times < 1) return fail(NB200_EINVAL, "loop needs 0 <= start <= stop <= layers and times >= 1");
-    }
-    for (uint32_t i = 0; i < lo; i++) { Run q; q.layer = i; e->runs.push_back(q); }
-    for (uint32_t p = 0; p < times; p++) for (uint32_t i = lo; i < hi; i++) { Run q; q.layer = i; q.add_embed = p > 0 && i == lo; e->runs.push_back(q); if (q.add_embed) e->keep_x0 = true; }
-    for (uint32_t i = hi; i < NL; i++) { Run q; q.layer = i; e->runs.push_back(q); }
 
     // state manager: slots and pages
     e->max_tokens = max_tokens;
@@ -870,9 +1187,18 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     size_t off = 0;
     for (Run &q : e->runs) {
         const Layer &L = e->layers[q.layer];
-        q.st_prev = off; off += E;
-        if (L.type == MIX_RGLRU) { q.st_S = off; off += L.C; q.st_conv = off; off += (size_t)(L.taps - 1) * L.C; }
-        else { DM(q.cache, (size_t)e->n_pages * kPage * L.R * 4); }
+        if (e->form == FORM_PARALLEL_SHIFT) { q.st_prev = off; off += E; }
+        switch (L.type) {
+            case MIX_RGLRU: q.st_S = off; off += L.C; q.st_conv = off; off += (size_t)(L.taps - 1) * L.C; break;
+            case MIX_LATENT_ATTN: DM(q.cache, (size_t)e->n_pages * kPage * L.R * 4); break;
+            case MIX_RETENTION: q.st_S = off; off += (size_t)L.H * L.vdim * L.dim; break;
+            default:          // window attention + selective scan: the tails of both convolutions, the scan state, a cache of key/value rows
+                q.st_conv = off; off += (size_t)(L.a_taps - 1) * (L.H + L.G) * L.dim;
+                q.st_conv2 = off; off += (size_t)(L.m_taps - 1) * L.mC;
+                q.st_S = off; off += (size_t)L.mC * L.mN;
+                DM(q.cache, (size_t)e->n_pages * kPage * L.RL * 4);
+                CK(cudaMemset(q.cache, 0, (size_t)e->n_pages * kPage * L.RL * 4));
+        }
     }
     e->slot_floats = (off + 3) & ~(size_t)3;
     DM(e->state, (size_t)e->max_seqs * e->slot_floats * 4);
@@ -885,10 +1211,35 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     // scratch for one chunk
     const size_t T = e->chunk_cap;
     uint32_t mC = 0, mZ = 0, mQR = 0, mQ = 0, mHR = 0, mOV = 0, mNE = 0, mTop = 0, mFF = 0, mSFF = 0;
+    uint32_t sP = 0, sQK = 0, sXC = 0, sA = 0, sRO = 0, sDBC = 0, sF = 0;
+    size_t win_smem[4] = {0, 0, 0, 0};      // most shared memory any layer asks of the window-attention instances, per value-column count
+    for (const Run &q : e->runs) {
+        const Layer &L = e->layers[q.layer];
+        if (L.type == MIX_RETENTION) { sP = std::max(sP, 2 * L.H * (L.dim + L.vdim)); sA = std::max(sA, L.H * L.vdim); sRO = std::max(sRO, L.H * L.vdim); }
+        if (L.type == MIX_WINDOW_SSM) {
+            sP = std::max(sP, (2 * L.H + L.G) * L.dim + 2 * L.mC); sQK = std::max(sQK, (L.H + L.G) * L.dim); sXC = std::max(sXC, L.mC); sA = std::max(sA, L.H * L.dim);
+            sDBC = std::max(sDBC, L.mR + 2 * L.mN);
+            const uint32_t qt = win_attn_qt(L);
+            if (!qt) return fail(NB200_EINVAL, "window attention with %u heads of %u does not fit the attention kernel's shared memory", L.H, L.dim);
+            size_t &sm = win_smem[L.dim <= 32 ? 0 : L.dim <= 64 ? 1 : L.dim <= 128 ? 2 : 3];
+            sm = std::max(sm, std::max(win_attn_smem(L.H, L.dim, L.RL, qt), win_attn_smem(L.H, L.dim, L.RL, 1)));
+        }
+        if (L.ff_kind == FF_DENSE_POLY) sF = std::max(sF, L.ff);
+    }
+    if (win_smem[0] > 48 * 1024 && (r = win_attn_optin_v<1>((int)win_smem[0]))) return r;
+    if (win_smem[1] > 48 * 1024 && (r = win_attn_optin_v<2>((int)win_smem[1]))) return r;
+    if (win_smem[2] > 48 * 1024 && (r = win_attn_optin_v<4>((int)win_smem[2]))) return r;
+    if (win_smem[3] > 48 * 1024 && (r = win_attn_optin_v<8>((int)win_smem[3]))) return r;
+    if (sP) DM(e->b_p, T * sP * 4);
+    if (sQK) { DM(e->b_qk, T * sQK * 4); DM(e->b_xc, T * sXC * 4); DM(e->b_dbc, T * sDBC * 4); DM(e->b_dt, T * sXC * 4); DM(e->b_y, T * sXC * 4); }
+    if (sA) DM(e->b_a, T * sA * 4);
+    if (sRO) DM(e->b_ro, T * sRO * 4);
+    if (sF) DM(e->b_f, T * sF * 4);
     for (const Layer &L : e->layers) {
+        if (L.type == MIX_RETENTION || L.type == MIX_WINDOW_SSM) continue;
         if (L.type == MIX_RGLRU) mC = std::max(mC, L.C);
         else { mZ = std::max(mZ, L.QR + L.R); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim); mHR = std::max(mHR, L.H * L.R); mOV = std::max(mOV, L.H * L.vdim); }
-        if (L.has_mlp) { mNE = std::max(mNE, L.NE); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
+        if (L.ff_kind == FF_MOE) { mNE = std::max(mNE, L.NE); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
     }
     DM(e->x, T * E * 4); DM(e->hm, T * E * 4); DM(e->h2, T * E * 4); DM(e->d, T * E * 4);
     if (e->keep_x0) DM(e->x0, T * E * 4);

@@ -36,7 +36,8 @@ constexpr uint32_t kPage = 32;            // tokens per cache page == keys per a
 constexpr uint32_t kAttnWarps = 8;        // heads per attention block
 constexpr uint32_t kGemvMaxM = 4;         // rows a k_gemv launch handles per group
 
-enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5 };
+enum CMode : uint32_t { C_ADD = 1, C_SCALE = 2 };
+enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5, EPI_SOFTPLUS = 6 };
 
 // C[r, c0 + n] = epi( sum_k A[arow(r), a0 + k] * W[g][n, k] + bias[g][n] )   for the rows r of group g
 //   rows of group g : [g_off[g], g_off[g+1])  when g_off is given (sizes known on the device only), else [0, M)
@@ -56,6 +57,9 @@ struct GemmArgs {
     // causal convolution over the rows in order (taps cv_taps[c][cv_K], bias cv_bias, tail cv_state [cv_K - 1][N - split]) whose
     // outputs go to cv_out [rows][N - split]; the tail moves on.  One warp owns a channel, so the tail has one reader and one writer.
     const float *cv_taps, *cv_bias; float *cv_state, *cv_out; uint32_t cv_K;
+    // After the epilogue: with c_mode & C_SCALE the value is multiplied by c_scale, with c_mode & C_ADD it is added to what C holds,
+    // so two products can be summed with fixed weights into one output (C = s1 A1 W1^T, then C += s2 A2 W2^T).
+    float c_scale; uint32_t c_mode;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -88,8 +92,13 @@ __device__ __forceinline__ float epilogue(float v, const GemmArgs &a, const floa
         case EPI_GELU_SPLIT: case EPI_GELU_CONV: return n < a.split ? gelu_tanh(v) : v;
         case EPI_SIGMOID: return sigmoidf_(v);
         case EPI_RELU2: { const float r = fmaxf(v, 0.0f); return r * r; }
+        case EPI_SOFTPLUS: return softplusf_(v);
         default: return v;
     }
+}
+__device__ __forceinline__ void store_c(const GemmArgs &a, float *dst, float v) {
+    if (a.c_mode & C_SCALE) v *= a.c_scale;
+    *dst = (a.c_mode & C_ADD) ? *dst + v : v;
 }
 
 struct GroupView { uint32_t r0, rows, a0, c0; const float *bias; uint64_t w0; };
@@ -157,7 +166,7 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const GemmArgs a) {
 #pragma unroll
         for (uint32_t j = 0; j < 4; j++) {
             const uint32_t n = n0 + tx * 4 + j;
-            if (n < a.N) a.C[(size_t)(gv.r0 + r) * a.ldc + gv.c0 + n] = epilogue(acc[i][j], a, gv.bias, n);
+            if (n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, epilogue(acc[i][j], a, gv.bias, n));
         }
     }
 }
@@ -260,7 +269,7 @@ __global__ void __launch_bounds__(128) k_gemm_bf16(const GemmArgs a) {
 #pragma unroll
             for (uint32_t q = 0; q < 4; q++) {
                 const uint32_t r = m0 + wm + i * 16 + g + (q >> 1) * 8, n = n0 + wn + j * 8 + 2 * t + (q & 1u);
-                if (r < gv.rows && n < a.N) a.C[(size_t)(gv.r0 + r) * a.ldc + gv.c0 + n] = epilogue(acc[i][j][q], a, gv.bias, n);
+                if (r < gv.rows && n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, epilogue(acc[i][j][q], a, gv.bias, n));
             }
 }
 
@@ -394,7 +403,7 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
         }
 #pragma unroll
         for (uint32_t i = 0; i < kGemvMaxM; i++)
-            if (i < rows) a.C[(size_t)(gv.r0 + i) * a.ldc + gv.c0 + n] = epilogue(acc[i], a, gv.bias, n);
+            if (i < rows) store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, epilogue(acc[i], a, gv.bias, n));
     }
 }
 
@@ -484,19 +493,21 @@ __global__ void __launch_bounds__(256) k_norm_shift(const NormShiftArgs a) {
 
 // causal per-channel convolution: u[t,c] = b[c] + sum_j taps[c,j] * v[t - (K-1-j), c]; inputs before this portion come from the
 // state (the last K-1 inputs of the sequence so far, oldest first; zeros at the start)
-struct ConvArgs { const float *v; uint32_t ldv; const float *taps, *bias; float *state; float *u; uint32_t T, C, K; };
+// bias may be null; ldu: row stride of u (0: C); act 1: silu on the output
+struct ConvArgs { const float *v; uint32_t ldv; const float *taps, *bias; float *state; float *u; uint32_t T, C, K; uint32_t ldu, act; };
 __global__ void k_conv(const ConvArgs a) {
     pdl_enter();
     const size_t total = (size_t)a.T * a.C;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / a.C), c = (uint32_t)(i % a.C);
-        float s = a.bias[c];
+        float s = a.bias ? a.bias[c] : 0.0f;
         for (uint32_t j = 0; j < a.K; j++) {
             const int64_t src = (int64_t)t - (int64_t)(a.K - 1 - j);
             const float v = src >= 0 ? a.v[(size_t)src * a.ldv + c] : a.state[(size_t)((int64_t)(a.K - 1) + src) * a.C + c];
             s = fmaf(a.taps[(size_t)c * a.K + j], v, s);
         }
-        a.u[i] = s;
+        if (a.act) s = s / (1.0f + expf(-s));
+        a.u[(size_t)t * (a.ldu ? a.ldu : a.C) + c] = s;
     }
 }
 // after k_conv: the tail becomes the last K-1 inputs, this portion included
@@ -990,8 +1001,9 @@ __global__ void k_combine(const CombineArgs a) {
 }
 
 // scalar-gain RMS norm of the rows whose logits are asked for: out[i] = x[want[i]] / rms * g
+// (vec: the gain is a vector stored around zero, out = x / rms * (1 + g[i]))
 __global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x, const uint32_t *__restrict__ want, const float *__restrict__ g,
-                                                    float *__restrict__ out, uint32_t E, float eps) {
+                                                    float *__restrict__ out, uint32_t E, float eps, uint32_t vec) {
     pdl_enter();
     __shared__ float red[32];
     const float *xt = x + (size_t)want[blockIdx.x] * E;
@@ -999,8 +1011,8 @@ __global__ void __launch_bounds__(256) k_final_norm(const float *__restrict__ x,
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) s = fmaf(xt[i], xt[i], s);
     s = block_sum(s, red);
     const float rinv = 1.0f / sqrtf(s / (float)E + eps) * 1.0f;
-    const float gv = *g;
-    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)blockIdx.x * E + i] = xt[i] * rinv * gv;
+    const float gv = vec ? 0.0f : *g;
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)blockIdx.x * E + i] = xt[i] * rinv * (vec ? 1.0f + g[i] : gv);
 }
 
 // greedy choice with the repetition penalty of the generation hosts: logits of ids seen before are divided (positive) or multiplied

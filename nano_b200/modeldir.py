@@ -1,5 +1,5 @@
-"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra models for the
-benchmarks and tests.  The reader the engine uses is native (csrc/modeldir.cu); nothing here is on the compute path.
+"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra and Rakarax models for
+the benchmarks and tests.  The reader the engine uses is native (csrc/modeldir.cu); nothing here is on the compute path.
 
 A safetensors file is an 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets) and
 the tensor bytes.
@@ -113,4 +113,68 @@ def famudra_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, 
                 t[p + f"mlp.e{e}.up"] = lin(f["expert"]["ff"], E); t[p + f"mlp.e{e}.down"] = lin(E, f["expert"]["ff"])
             if f.get("shared"):
                 t[p + "mlp.shared.up"] = lin(f["shared"]["ff"], E); t[p + "mlp.shared.down"] = lin(E, f["shared"]["ff"])
+    return t
+
+
+def rakarax_config(vocab: int, width: int, layers, max_positions: int = 512, eps: float = 1e-5) -> dict:
+    """layers: list of (type, mixer, ff) or (type, mixer, ff, weights_of).
+    type "retention": mixer {heads, dim, vdim, decay: [per head], rot: {dims, base} or None};
+    type "parallel": mixer {left: {heads, kv_heads, dim, vdim, conv, scale, softcap, mask: {size} or None}, right: {inner, state,
+    dt_rank, conv}, left_scale, right_scale}; ff: width of the dense feed-forward, or None for a layer without one.
+    A layer with weights_of = j repeats layer j's entry and has no tensors of its own."""
+    out = []
+    for ent in layers:
+        kind, mixer, ff = ent[:3]
+        L = {"type": kind, "mixer": json.loads(json.dumps(mixer)), "mlp": {"kind": "dense", "ff": ff} if ff else None}
+        if len(ent) > 3 and ent[3] is not None:
+            L["weights_of"] = int(ent[3])
+        out.append(L)
+    return {"architecture": "Rakarax", "vocab": vocab, "width": width, "max_positions": max_positions, "norm": {"eps": eps}, "layers": out}
+
+
+def rakarax_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, np.ndarray]:
+    """Random weights (bfloat16-representable fp32 arrays) for a Rakarax config: projections ~ N(0, gain^2 / fan_in)."""
+    rng = np.random.default_rng(seed)
+    E, V = config["width"], config["vocab"]
+
+    def lin(o, i, g=1.0):
+        return bf16_round((rng.standard_normal((o, i), dtype=np.float32) * (gain * g / np.sqrt(i))).astype(np.float32))
+
+    def vecn(n, lo, hi):
+        return bf16_round(rng.uniform(lo, hi, size=n).astype(np.float32))
+
+    t = {"embed": bf16_round(rng.standard_normal((V, E), dtype=np.float32)),
+         "pos": bf16_round(0.5 * rng.standard_normal((config["max_positions"], E), dtype=np.float32)),
+         "head": lin(V, E), "final.norm": vecn(E, -0.2, 0.2)}
+    for i, L in enumerate(config["layers"]):
+        if "weights_of" in L:
+            continue
+        p = f"l{i}."
+        for n in ("norm1", "norm1b"):
+            t[p + n] = vecn(E, -0.2, 0.2)
+        m = L["mixer"]
+        if L["type"] == "retention":
+            H, D, VD = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"] = lin(H * D, E, 2.0); t[p + "mix.k"] = lin(H * D, E, 2.0)
+            t[p + "mix.v"] = lin(H * VD, E); t[p + "mix.g"] = lin(H * VD, E, 2.0); t[p + "mix.o"] = lin(E, H * VD)
+        else:
+            a, r = m["left"], m["right"]
+            H, G, D = a["heads"], a["kv_heads"], a["dim"]
+            t[p + "mix.left.q"] = lin(H * D, E); t[p + "mix.left.k"] = lin(G * D, E)
+            t[p + "mix.left.q.conv"] = vecn((H * D, a["conv"]), -0.6, 0.6); t[p + "mix.left.k.conv"] = vecn((G * D, a["conv"]), -0.6, 0.6)
+            t[p + "mix.left.talk"] = bf16_round((np.eye(H) + 0.3 * rng.standard_normal((H, H))).astype(np.float32))
+            t[p + "mix.left.temp"] = vecn(H, 0.5, 2.0)
+            t[p + "mix.left.g"] = lin(H * a["vdim"], E, 2.0); t[p + "mix.left.o"] = lin(E, H * a["vdim"])
+            C, N, R = r["inner"], r["state"], r["dt_rank"]
+            t[p + "mix.right.in"] = lin(2 * C, E)
+            t[p + "mix.right.conv"] = vecn((C, r["conv"]), -0.6, 0.6); t[p + "mix.right.conv.b"] = vecn(C, -0.1, 0.1)
+            t[p + "mix.right.x"] = lin(R + 2 * N, C); t[p + "mix.right.dt"] = lin(C, R, 2.0); t[p + "mix.right.dt.b"] = vecn(C, -4.0, -1.0)
+            t[p + "mix.right.A_log"] = bf16_round(np.log(rng.uniform(0.5, 8.0, size=(C, N))).astype(np.float32))
+            t[p + "mix.right.D"] = vecn(C, 0.5, 1.5); t[p + "mix.right.o"] = lin(E, C)
+        f = L.get("mlp")
+        if f:
+            for n in ("norm2", "norm2b"):
+                t[p + n] = vecn(E, -0.2, 0.2)
+            t[p + "mlp.up"] = lin(f["ff"], E, 1.5); t[p + "mlp.down"] = lin(E, f["ff"])
+            t[p + "mlp.act"] = bf16_round(np.array([0.6, 0.3, 0.15, 0.05], np.float32) * rng.uniform(0.7, 1.3, size=4).astype(np.float32))
     return t

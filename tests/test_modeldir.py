@@ -44,3 +44,31 @@ def test_bf16_writer_rounds_to_nearest_even():
     a = np.array([1.0, 1.00390625, 1.01171875, -3.1415927, 0.0], np.float32)     # 1 + 2^-8 is a tie: even mantissa wins
     r = md.bf16_round(a)
     assert r[0] == 1.0 and r[1] == 1.0 and r[2] == np.float32(1.015625) and abs(r[3] + 3.140625) < 1e-6
+
+
+@pytest.mark.skipif(E.device_count() > 0, reason="box has a GPU")
+def test_rakarax_folder_reaches_the_layered_family(tmp_path):
+    ret = {"heads": 1, "dim": 8, "vdim": 8, "decay": [0.9], "rot": {"dims": 4, "base": 100.0}}
+    cfg = md.rakarax_config(16, 8, [("retention", ret, 12), ("retention", ret, 12, 0)], max_positions=32)
+    w = md.rakarax_random(cfg)
+    assert not any(k.startswith("l1.") for k in w)            # a layer with weights_of has no tensors of its own
+    p = md.write_model_dir(str(tmp_path / "r"), cfg, w)
+    with pytest.raises(E.NB200Error, match="no CUDA device"):
+        E.Engine(p, 16)
+
+
+def test_rakarax_oracle_is_causal_and_windowed():
+    """The plain restatement itself: a prefix gives the same logits, and a token outside every window, decay 0 and a scan that
+    forgets at once leaves no trace."""
+    from rakarax_oracle import forward
+    left = {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "conv": 2, "scale": 0.4, "softcap": 10.0, "mask": {"size": 3}}
+    right = {"inner": 12, "state": 3, "dt_rank": 2, "conv": 2}
+    cfg = md.rakarax_config(20, 16, [("parallel", {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.0}, 8)], max_positions=32)
+    w = md.rakarax_random(cfg, 3)
+    t = np.random.default_rng(0).integers(0, 20, 24)
+    full = forward(cfg, w, t)
+    assert np.allclose(forward(cfg, w, t[:10]), full[:10], atol=1e-12)
+    t2 = t.copy(); t2[5] = (t2[5] + 1) % 20
+    other = forward(cfg, w, t2)
+    # window 3 and two taps: position 5 reaches positions 5 .. 5 + 2 + 1 through the attention, not beyond
+    assert np.abs(other[5] - full[5]).max() > 1e-6 and np.allclose(other[9:], full[9:], atol=1e-12)
