@@ -530,6 +530,35 @@ def famudra_flops_per_token(cfg, ctx):
         4.0 * L["mixer"]["heads"] * L["mixer"]["kv_rank"] * ctx for L in cfg["layers"] if L["type"] == "latent_attention")
 
 
+def layered_modes(E, path, vocab, ctx, n_dec, T, args, hbm, tf, bytes_fn, flops_fn, max_pos=None):
+    """Decode and prefill timings of one model folder in bf16 (and, with --with-f32, in true 32-bit)."""
+    rng = np.random.default_rng(0)
+    row = {}
+    for mode, flags in (("bf16", 0), ("f32", E.FLAG_F32)):
+        if mode == "f32" and not args.with_f32:
+            continue
+        eng = E.Engine(path, ctx + n_dec + T + 64, flags=flags)
+        ids = np.zeros(ctx + n_dec + 8, np.uint32); ids[:ctx] = rng.integers(0, vocab, ctx)
+        for _ in range(max(1, min(args.warmup, 3))):
+            eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
+        l0 = eng.launches
+        pre_ms, dec_ms = eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
+        launches = eng.launches - l0
+        s = eng.seq_open()
+        pf_ms = eng.step_timed(s, rng.integers(0, vocab, T).astype(np.uint32), max(1, args.steps))
+        eng.seq_close(s)
+        wb = 2 if mode == "bf16" else 4
+        bts = bytes_fn(ctx + n_dec / 2, wb)
+        fl = flops_fn(T / 2)
+        row[mode] = {"decode_tok_s": n_dec / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / n_dec, "decode_bytes_per_token": bts,
+                     "decode_hbm_frac": bts * n_dec / (dec_ms * 1e-3) / (hbm * 1e9), "launches_per_token": eng.launches_per_token,
+                     "prefill_tok_s": T / (pf_ms * 1e-3), "prefill_portion": T, "prefill_tflops": fl * T / (pf_ms * 1e-3) / 1e12,
+                     "prefill_frac_of_bf16_peak": fl * T / (pf_ms * 1e-3) / 1e12 / tf if mode == "bf16" else None,
+                     "prompt_1024_ms": pre_ms, "gpu_launches": int(launches), "weight_bytes": eng.weight_bytes}
+        eng.close()
+    return row
+
+
 def famudra_bench(args):
     from nano_b200 import engine as E
     hbm, hbm_src = peaks()
@@ -543,29 +572,7 @@ def famudra_bench(args):
     for name in (args.sizes.split(",") if args.sizes else sorted(FAMUDRA_SIZES)):
         path, cfg = famudra_model(name)
         rng = np.random.default_rng(0)
-        row = {}
-        for mode, flags in (("bf16", 0), ("f32", E.FLAG_F32)):
-            if mode == "f32" and not args.with_f32:
-                continue
-            eng = E.Engine(path, ctx + n_dec + T + 64, flags=flags)
-            ids = np.zeros(ctx + n_dec + 8, np.uint32); ids[:ctx] = rng.integers(0, FAMUDRA_VOCAB, ctx)
-            for _ in range(max(1, min(args.warmup, 3))):
-                eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
-            l0 = eng.launches
-            pre_ms, dec_ms = eng.decode_greedy(ids.copy(), ctx, ctx + n_dec)
-            launches = eng.launches - l0
-            s = eng.seq_open()
-            pf_ms = eng.step_timed(s, rng.integers(0, FAMUDRA_VOCAB, T).astype(np.uint32), max(1, args.steps))
-            eng.seq_close(s)
-            wb = 2 if mode == "bf16" else 4
-            bts = famudra_decode_bytes(cfg, ctx + n_dec / 2, wb)
-            fl = famudra_flops_per_token(cfg, T / 2)
-            row[mode] = {"decode_tok_s": n_dec / (dec_ms * 1e-3), "decode_ms_per_token": dec_ms / n_dec, "decode_bytes_per_token": bts,
-                         "decode_hbm_frac": bts * n_dec / (dec_ms * 1e-3) / (hbm * 1e9), "launches_per_token": eng.launches_per_token,
-                         "prefill_tok_s": T / (pf_ms * 1e-3), "prefill_portion": T, "prefill_tflops": fl * T / (pf_ms * 1e-3) / 1e12,
-                         "prefill_frac_of_bf16_peak": fl * T / (pf_ms * 1e-3) / 1e12 / tf if mode == "bf16" else None,
-                         "prompt_1024_ms": pre_ms, "gpu_launches": int(launches), "weight_bytes": eng.weight_bytes}
-            eng.close()
+        row = layered_modes(E, path, FAMUDRA_VOCAB, ctx, n_dec, T, args, hbm, tf, lambda pos, wb: famudra_decode_bytes(cfg, pos, wb), lambda c: famudra_flops_per_token(cfg, c))
         # the closest model of the engine: Qwen3 architecture, same width and depth, Q80 model file; its prompt runs position by position
         E_, L = FAMUDRA_SIZES[name][0], FAMUDRA_SIZES[name][1]
         spec = mf.ModelSpec(f"peer-{name}", mf.ARCH_QWEN3, ctx + n_dec + 8, FAMUDRA_VOCAB, L, E_, 16, 8, FAMUDRA_SIZES[name][-1], 128)
@@ -585,6 +592,88 @@ def famudra_bench(args):
                       "clocks": clocks, "sizes": out}))
 
 
+# --------------------------------------------------------------------------------------------------
+# --design rakarax: the same two measurements for the Rakarax design (retention and window-attention + selective-scan layers, dense
+# PolyNorm feed-forward) beside the closest model of the same runtime, Famudra, at equal width and depth.
+# --------------------------------------------------------------------------------------------------
+RAKARAX_SIZES = {
+    # name: (width, layers, attention heads, kv heads, head dim, window, scan inner, scan state, dt rank, retention heads, dim, vdim, ff)
+    "w1024": (1024, 8, 16, 4, 64, 512, 2048, 16, 64, 8, 128, 256, 3072),
+    "w2048": (2048, 8, 16, 4, 128, 1024, 4096, 16, 128, 16, 128, 256, 6144),
+}
+RAKARAX_POSITIONS = 4096
+
+
+def rakarax_model(name):
+    from nano_b200 import modeldir as md
+    E_, L, H, G, D, W, C, N, R, RH, RD, RVD, ff = RAKARAX_SIZES[name]
+    par = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "conv": 4, "scale": D ** -0.5, "softcap": 30.0, "mask": {"size": W}},
+           "right": {"inner": C, "state": N, "dt_rank": R, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}
+    ret = {"heads": RH, "dim": RD, "vdim": RVD, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, RH - 1)) for h in range(RH)], "rot": {"dims": RD, "base": 10000.0}}
+    layers = [("parallel", par, ff) if i % 2 == 0 else ("retention", ret, ff) for i in range(L)]
+    cfg = md.rakarax_config(FAMUDRA_VOCAB, E_, layers, max_positions=RAKARAX_POSITIONS)
+    path = os.path.join(os.environ.get("NB200_MODEL_CACHE", "/tmp/nb200_models"), f"rakarax-{name}")
+    if not os.path.exists(os.path.join(path, "model.safetensors")):
+        md.write_model_dir(path + ".part", cfg, md.rakarax_random(cfg, 0))
+        os.replace(path + ".part", path)
+    return path, cfg
+
+
+def rakarax_decode_bytes(cfg, pos, wbytes=2):
+    """Algorithmic HBM bytes of one decoded token at position pos: every matrix once, the fp32 states read and written, the fp32
+    key/value rows inside the window, the head."""
+    E_ = cfg["width"]; b = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "retention":
+            H, D, VD = m["heads"], m["dim"], m["vdim"]
+            b += wbytes * (2 * H * D + 3 * H * VD) * E_ + 8.0 * H * D * VD
+        else:
+            a, r = m["left"], m["right"]
+            H, G, D, C, N, R = a["heads"], a["kv_heads"], a["dim"], r["inner"], r["state"], r["dt_rank"]
+            keys = min(pos + 1, a["mask"]["size"]) if a.get("mask") else pos + 1
+            b += wbytes * ((3 * H * D + G * D + 3 * C) * E_ + (R + 2 * N) * C + C * R) + 8.0 * C * N + 4.0 * (G * D + G) * keys
+        if L.get("mlp"):
+            b += wbytes * 2 * E_ * L["mlp"]["ff"]
+    return b + wbytes * cfg["vocab"] * E_
+
+
+def rakarax_flops_per_token(cfg, ctx):
+    fl = 2.0 * (rakarax_decode_bytes(cfg, 0, 1) - cfg["vocab"] * cfg["width"])
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "retention":
+            fl += 4.0 * m["heads"] * m["dim"] * m["vdim"]
+        else:
+            a, r = m["left"], m["right"]
+            fl += 4.0 * a["heads"] * a["dim"] * min(ctx, a["mask"]["size"] if a.get("mask") else ctx) + 6.0 * r["inner"] * r["state"]
+    return fl
+
+
+def rakarax_bench(args):
+    from nano_b200 import engine as E
+    hbm, hbm_src = peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    ctx, n_dec, T = 1024, 128, 2048
+    sampler = ClockSampler(0); sampler.start()
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else sorted(RAKARAX_SIZES)):
+        path, cfg = rakarax_model(name)
+        row = layered_modes(E, path, FAMUDRA_VOCAB, ctx, n_dec, T, args, hbm, tf, lambda pos, wb: rakarax_decode_bytes(cfg, pos, wb), lambda c: rakarax_flops_per_token(cfg, c))
+        ppath, pcfg = famudra_model(name)          # the closest model: the same runtime's Famudra at equal width and depth
+        args_bf16 = argparse.Namespace(**{**vars(args), "with_f32": False})
+        row["peer_famudra"] = layered_modes(E, ppath, FAMUDRA_VOCAB, ctx, n_dec, T, args_bf16, hbm, tf, lambda pos, wb: famudra_decode_bytes(pcfg, pos, wb), lambda c: famudra_flops_per_token(pcfg, c))["bf16"]
+        out[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "rakarax", "unit": "tokens/s", "n_gpus": 1, "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf},
+                      "config": {"decode": f"greedy device loop, {n_dec} tokens after a {ctx}-token prompt, batch 1", "prefill": f"one portion of {T} tokens into an empty sequence",
+                                 "timing": "CUDA events on the engine's stream after warm-up", "l2": "fractions are against HBM although the weights of one token fit the 126 MB L2 at w1024"},
+                      "clocks": clocks, "sizes": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -601,12 +690,15 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-stream", action="store_true", help="forbid the streaming kernel")
-    ap.add_argument("--design", default=None, choices=["famudra"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
+    ap.add_argument("--design", default=None, choices=["famudra", "rakarax"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
     ap.add_argument("--sizes", default=None, help="--design: comma-separated size names (default: all)")
     ap.add_argument("--with-f32", action="store_true", help="--design: also time the true-32-bit mode")
     args = ap.parse_args()
     if args.design == "famudra":
         famudra_bench(args)
+        return
+    if args.design == "rakarax":
+        rakarax_bench(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

@@ -349,6 +349,12 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
 // (at most 4 per lane).  Per token:  S[c][n] <- exp(dt_c A[c][n]) S[c][n] + (dt_c x_c) B_n,  y_c = sum_n S[c][n] C_n + D_c x_c,
 // out = y_c silu(z_c).  dt [T][C] is the step size after its softplus, x [T][C] the convolved, activated input, B and C sit in the
 // rows of bc at columns b0 and c0, A = -exp(A_log) [C][N].
+// exp(z) S + b for z <= 0.  A slowly decaying state takes thousands of these steps, and the error of expf (two units in the last
+// place of a number near 1) would be several times the rounding of the sum itself; for small |z| the decay is taken as 1 + expm1(z),
+// whose error is relative to |z|, and applied as S + (expm1(z) S + b).
+__device__ __forceinline__ float decay_drive(float z, float S, float b) {
+    return z > -0.25f ? S + fmaf(expm1f(z), S, b) : fmaf(expf(z), S, b);
+}
 struct SelScanArgs { const float *dt; const float *x; const float *bc; uint32_t ldb, b0, c0; const float *A, *Dv; const float *z; uint32_t ldz;
                      float *S; float *y; uint32_t T, C, N; };
 template <int LG>
@@ -373,7 +379,7 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
         for (int k = 0; k < 4; k++) {
             const uint32_t n = g + LG * k;
             if (n < a.N) {
-                S[k] = fmaf(expf(dtc * Av[k]), S[k], dx * row[a.b0 + n]);
+                S[k] = decay_drive(dtc * Av[k], S[k], dx * row[a.b0 + n]);
                 acc = fmaf(S[k], row[a.c0 + n], acc);
             }
         }

@@ -76,7 +76,9 @@ def in_cuts(eng, t, cuts):
     s = eng.seq_open()
     out, at = [], 0
     for c in cuts:
-        out.append(eng.step(s, t[at:at + c], range(len(t[at:at + c]))))
+        part = t[at:at + c]
+        if len(part):
+            out.append(eng.step(s, part, range(len(part))))
         at += c
     eng.seq_close(s)
     assert at >= len(t)
@@ -125,7 +127,7 @@ def test_feed_forward(tmp_path, ff):
     ref = oracle_forward(cfg, w, t, np.float64, trace)
     assert rel(whole(eng, t), ref) < F32_TOL
     assert np.abs(eng.read_residual(0, len(t)) - trace[0]).max() <= 3e-5 * np.abs(trace[0]).max()
-    assert rel(in_cuts(eng, t, [1] * 20), ref[:20]) < F32_TOL
+    assert rel(in_cuts(eng, t[:20], [1] * 20), ref[:20]) < F32_TOL
     eng.close()
 
 
