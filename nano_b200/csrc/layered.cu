@@ -116,6 +116,7 @@ struct LayeredEngine : nb::EngineBase {
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
     float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
+    float *b_wpart = nullptr; uint32_t *b_wtick = nullptr;      // window attention: partials and tickets of the key splits
     float *b_p = nullptr, *b_qk = nullptr, *b_xc = nullptr, *b_a = nullptr, *b_ro = nullptr, *b_dbc = nullptr, *b_dt = nullptr, *b_y = nullptr, *b_f = nullptr;   // retention, window attention + selective scan, dense feed-forward
     uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
@@ -532,7 +533,7 @@ int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
     RopeArgs ra{e->b_p, P, 0, H * D, T, H, D, L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr};
     if ((r = launch<RopeArgs>(e, k_rope, dim3(ew_grid((size_t)T * H * (D - L.rot_dims / 2u))), dim3(256), 0, ra))) return r;
     RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD};
-    const dim3 grid((H * VD + 7u) / 8u), block(256);
+    const dim3 grid((VD + kRetCols - 1u) / kRetCols, H), block(256);
     if (D <= 32) r = launch<RetentionArgs>(e, k_retention_scan<1>, grid, block, 0, sa);
     else if (D <= 64) r = launch<RetentionArgs>(e, k_retention_scan<2>, grid, block, 0, sa);
     else if (D <= 128) r = launch<RetentionArgs>(e, k_retention_scan<4>, grid, block, 0, sa);
@@ -546,7 +547,7 @@ int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
 template <int VCH>
 int win_attn_launch_v(LayeredEngine *e, const WinAttnArgs &a, uint32_t qt, uint32_t hs) {
     const uint32_t warps = (a.H + hs - 1) / hs;
-    const dim3 grid((a.T + qt - 1) / qt), block(warps * 32);
+    const dim3 grid((a.T + qt - 1) / qt, a.nsplit), block(warps * 32);
     const size_t smem = win_attn_smem(a.H, a.D, a.RL, qt);
     if (hs == 1) {
         if (qt == 8) return launch<WinAttnArgs>(e, k_window_attn<VCH, 8, 1>, grid, block, smem, a);
@@ -582,6 +583,7 @@ int win_attn_launch(LayeredEngine *e, const Layer &L, const WinAttnArgs &a) {
 
 template <int LG>
 int sel_scan_launch(LayeredEngine *e, const SelScanArgs &a) {
+    if (a.T > 32) return launch<SelScanArgs>(e, k_selective_scan_par<LG>, dim3(((size_t)a.C * LG + 31u) / 32u), dim3(32, a.T >= 256 ? 32 : 8), 0, a);
     return launch<SelScanArgs>(e, k_selective_scan<LG>, dim3(((size_t)a.C * LG + 255u) / 256u), dim3(256), 0, a);
 }
 
@@ -605,7 +607,12 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
     // left
     QkPrepArgs qa{e->b_qk, QK, e->b_qk + H * D, QK, L.temp, L.scale, run.cache, cx.table, H, G, D, L.RL, cx.pos0, e->eps, cx.pos_ptr};
     if ((r = launch<QkPrepArgs>(e, k_qk_prepare, dim3(T), dim3(256), 0, qa))) return r;
-    WinAttnArgs wa{e->b_qk, QK, run.cache, cx.table, e->b_p + g0, P, L.talk, L.slopes, e->b_a, T, H, G, D, L.RL, cx.pos0, L.window, L.softcap, cx.pos_ptr};
+    WinAttnArgs wa{e->b_qk, QK, run.cache, cx.table, e->b_p + g0, P, L.talk, L.slopes, e->b_a, T, H, G, D, L.RL, cx.pos0, L.window, L.softcap, cx.pos_ptr, 1u, e->b_wpart, e->b_wtick};
+    if (T <= kGemvMaxM) {      // short portions: the key pages of the window are dealt out to several blocks (two pages each at least)
+        const uint32_t reach = cx.pos_ptr ? e->max_tokens : cx.pos0 + T;      // a captured step does not know the position: the most pages a window can span
+        const uint32_t pages = std::min(reach, L.window + T) / kPage + 1u;
+        wa.nsplit = std::max(1u, std::min(kSplitMax, pages / 2u));
+    }
     if ((r = win_attn_launch(e, L, wa))) return r;
     // right
     if ((r = gemm(e, plain(e->b_xc, C, L.xw, e->b_dbc, R + 2 * N, T), 1, T))) return r;
@@ -1231,6 +1238,13 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     if (win_smem[2] > 48 * 1024 && (r = win_attn_optin_v<4>((int)win_smem[2]))) return r;
     if (win_smem[3] > 48 * 1024 && (r = win_attn_optin_v<8>((int)win_smem[3]))) return r;
     if (sP) DM(e->b_p, T * sP * 4);
+    if (sQK) {
+        uint32_t mPart = 0;
+        for (const Run &q : e->runs) { const Layer &L = e->layers[q.layer]; if (L.type == MIX_WINDOW_SSM) mPart = std::max(mPart, L.H * (L.dim + 2)); }
+        DM(e->b_wpart, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
+        DM(e->b_wtick, (size_t)kGemvMaxM * 4);
+        CK(cudaMemset(e->b_wtick, 0, (size_t)kGemvMaxM * 4));
+    }
     if (sQK) { DM(e->b_qk, T * sQK * 4); DM(e->b_xc, T * sXC * 4); DM(e->b_dbc, T * sDBC * 4); DM(e->b_dt, T * sXC * 4); DM(e->b_y, T * sXC * 4); }
     if (sA) DM(e->b_a, T * sA * 4);
     if (sRO) DM(e->b_ro, T * sRO * 4);

@@ -96,36 +96,59 @@ __global__ void k_rope(const RopeArgs a) {
     }
 }
 
-// Retention, token by token: one warp owns value column j of head h and keeps S[h][:, j] in registers (lane l holds key
-// coordinates l, l + 32, ...); per token S <- decay_h S + k v_j and o_j = S . q.  p rows hold q at q0, k at k0 (already rotated and
-// scaled), v at v0.  The state is [H][VD][D] fp32; o is [T][H * VD].
+// Retention, token by token.  A block of 8 warps owns kRetCols value columns of head h = blockIdx.y (a warp kRetCpw of them) and
+// keeps S[h][:, j] in registers (lane l holds key coordinates l, l + 32, ...); per token S <- decay_h S + k v_j and o_j = S . q.
+// q, k (already rotated and scaled) and v of kRetTile tokens at a time are staged in shared memory, read there by every warp.
+// p rows hold q at q0, k at k0, v at v0.  The state is [H][VD][D] fp32; o is [T][H * VD].
 struct RetentionArgs { const float *p; uint32_t ld, q0, k0, v0; const float *decay; float *S; float *o; uint32_t T, H, D, VD; };
+constexpr uint32_t kRetCpw = 4, kRetCols = 8 * kRetCpw, kRetTile = 16;
 template <int DCH>
 __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
     pdl_enter();
-    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
-    if (warp >= a.H * a.VD) return;
-    const uint32_t h = warp / a.VD, j = warp % a.VD;
-    float *Sp = a.S + (size_t)warp * a.D;
-    float S[DCH];
+    __shared__ float qs[kRetTile][DCH * 32], ks[kRetTile][DCH * 32], vs[kRetTile][kRetCols];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = blockIdx.y, j0 = blockIdx.x * kRetCols, jw = j0 + warp * kRetCpw;
+    float S[kRetCpw][DCH];
 #pragma unroll
-    for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; S[c] = d < a.D ? Sp[d] : 0.0f; }
+    for (uint32_t i = 0; i < kRetCpw; i++)
+#pragma unroll
+        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; S[i][c] = (jw + i < a.VD && d < a.D) ? a.S[((size_t)h * a.VD + jw + i) * a.D + d] : 0.0f; }
     const float g = a.decay[h];
-    const float *qp = a.p + a.q0 + h * a.D, *kp = a.p + a.k0 + h * a.D, *vp = a.p + a.v0 + h * a.VD + j;
-    for (uint32_t t = 0; t < a.T; t++) {
-        const size_t ro = (size_t)t * a.ld;
-        const float v = vp[ro];
-        float acc = 0.0f;
-#pragma unroll
-        for (int c = 0; c < DCH; c++) {
-            const uint32_t d = lane + 32u * c;
-            if (d < a.D) { S[c] = fmaf(g, S[c], kp[ro + d] * v); acc = fmaf(S[c], qp[ro + d], acc); }
+    for (uint32_t t0 = 0; t0 < a.T; t0 += kRetTile) {
+        const uint32_t nt = min(kRetTile, a.T - t0);
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < nt * DCH * 32u; i += blockDim.x) {
+            const uint32_t t = i / (DCH * 32u), d = i % (DCH * 32u);
+            const float *row = a.p + (size_t)(t0 + t) * a.ld;
+            qs[t][d] = d < a.D ? row[a.q0 + h * a.D + d] : 0.0f;
+            ks[t][d] = d < a.D ? row[a.k0 + h * a.D + d] : 0.0f;
         }
-        acc = warp_sum(acc);
-        if (lane == 0) a.o[(size_t)t * a.H * a.VD + warp] = acc;
+        for (uint32_t i = threadIdx.x; i < nt * kRetCols; i += blockDim.x) {
+            const uint32_t t = i / kRetCols, j = i % kRetCols;
+            vs[t][j] = j0 + j < a.VD ? a.p[(size_t)(t0 + t) * a.ld + a.v0 + h * a.VD + j0 + j] : 0.0f;
+        }
+        __syncthreads();
+        for (uint32_t t = 0; t < nt; t++) {
+            float acc[kRetCpw], v[kRetCpw];
+#pragma unroll
+            for (uint32_t i = 0; i < kRetCpw; i++) { acc[i] = 0.0f; v[i] = vs[t][warp * kRetCpw + i]; }
+#pragma unroll
+            for (int c = 0; c < DCH; c++) {
+                const float kd = ks[t][lane + 32 * c], qd = qs[t][lane + 32 * c];
+#pragma unroll
+                for (uint32_t i = 0; i < kRetCpw; i++) { S[i][c] = fmaf(g, S[i][c], kd * v[i]); acc[i] = fmaf(S[i][c], qd, acc[i]); }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < kRetCpw; i++) acc[i] = warp_sum(acc[i]);
+            float mine = acc[0];
+#pragma unroll
+            for (uint32_t i = 1; i < kRetCpw; i++) if (lane == i) mine = acc[i];
+            if (lane < kRetCpw && jw + lane < a.VD) a.o[(size_t)(t0 + t) * a.H * a.VD + h * a.VD + jw + lane] = mine;
+        }
     }
 #pragma unroll
-    for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; if (d < a.D) Sp[d] = S[c]; }
+    for (uint32_t i = 0; i < kRetCpw; i++)
+#pragma unroll
+        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; if (jw + i < a.VD && d < a.D) a.S[((size_t)h * a.VD + jw + i) * a.D + d] = S[i][c]; }
 }
 
 // each head's o divided by its root mean square over the value columns, times silu(gate): a warp per (token, head)
@@ -188,6 +211,9 @@ struct WinAttnArgs {
     const float *q; uint32_t ldq; const float *cache; const uint32_t *table; const float *gate; uint32_t ldg;
     const float *talk, *slopes; float *out;
     uint32_t T, H, G, D, RL, pos0, window; float softcap; const uint32_t *pos_ptr;
+    // key splits (short portions): gridDim.y = nsplit blocks share a query tile's key pages and write partial (o, m, l) triples to
+    // part [T][nsplit][H][D + 2]; the block that draws the last ticket of its query tile (one zeroed counter each) merges them
+    uint32_t nsplit; float *part; uint32_t *tickets;
 };
 __host__ __device__ inline uint32_t win_attn_ldc(uint32_t RL) { return ((RL / 4u) & 1u) ? RL : RL + 4u; }      // rows of an odd number of 16-byte units
 __host__ __device__ inline uint32_t win_attn_qs(uint32_t H, uint32_t D, uint32_t qt) { return (qt * H * D + 3u) & ~3u; }
@@ -215,6 +241,8 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
     }
     const uint32_t p0 = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u) + tq0, last = p0 + nq - 1u;      // positions of the tile's first and last query
     const uint32_t tile_lo = p0 + 1u > a.window ? (p0 + 1u - a.window) / kPage : 0u, tile_hi = last / kPage;
+    const uint32_t tps = (tile_hi - tile_lo + a.nsplit) / a.nsplit;                         // key pages per split
+    const uint32_t my_lo = tile_lo + blockIdx.y * tps, my_hi = min(tile_hi + 1u, my_lo + tps);
     float m[HS][QT], l[HS][QT], o[HS][QT][VCH];
 #pragma unroll
     for (int hs = 0; hs < HS; hs++)
@@ -224,7 +252,7 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
 #pragma unroll
             for (int c = 0; c < VCH; c++) o[hs][qi][c] = 0.0f;
         }
-    for (uint32_t tile = tile_lo; tile <= tile_hi; tile++) {
+    for (uint32_t tile = my_lo; tile < my_hi; tile++) {
         __syncthreads();
         const uint32_t nk = min(kPage, last + 1u - tile * kPage);      // keys of this page that exist so far
         {
@@ -324,6 +352,56 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
             }
         }
     }
+    if (a.nsplit == 1) {
+#pragma unroll
+        for (int hs = 0; hs < HS; hs++) {
+            const uint32_t h = warp + hs * nw;
+            if (h >= H) continue;
+#pragma unroll
+            for (int qi = 0; qi < QT; qi++) {
+                if ((uint32_t)qi >= nq) continue;
+                const size_t t = tq0 + qi;
+                const float inv = 1.0f / l[hs][qi];
+#pragma unroll
+                for (int c = 0; c < VCH; c++) {
+                    const uint32_t r = lane + 32u * c;
+                    if (r >= D) continue;
+                    float v = o[hs][qi][c] * inv;
+                    if (a.gate) v *= sigmoidf_(a.gate[t * a.ldg + h * D + r]);
+                    a.out[t * HD + h * D + r] = v;
+                }
+            }
+        }
+        return;
+    }
+    // key splits: partial triples, then the last block of the query tile merges
+    //   out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s   over the splits that saw keys
+#pragma unroll
+    for (int hs = 0; hs < HS; hs++) {
+        const uint32_t h = warp + hs * nw;
+        if (h >= H) continue;
+#pragma unroll
+        for (int qi = 0; qi < QT; qi++) {
+            if ((uint32_t)qi >= nq) continue;
+            float *dst = a.part + (((size_t)(tq0 + qi) * a.nsplit + blockIdx.y) * H + h) * (D + 2u);
+#pragma unroll
+            for (int c = 0; c < VCH; c++) { const uint32_t r = lane + 32u * c; if (r < D) dst[r] = o[hs][qi][c]; }
+            if (lane == 0) { dst[D] = m[hs][qi]; dst[D + 1u] = l[hs][qi]; }
+        }
+    }
+    __shared__ uint32_t last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t *tk = a.tickets + blockIdx.x;
+        const uint32_t got = atomicAdd(tk, 1u);
+        last_s = got + 1u == a.nsplit;
+        if (last_s) *tk = 0u;              // ready for the next launch
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    const size_t stride = (size_t)H * (D + 2u);
 #pragma unroll
     for (int hs = 0; hs < HS; hs++) {
         const uint32_t h = warp + hs * nw;
@@ -332,12 +410,30 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
         for (int qi = 0; qi < QT; qi++) {
             if ((uint32_t)qi >= nq) continue;
             const size_t t = tq0 + qi;
-            const float inv = 1.0f / l[hs][qi];
+            const float *base = a.part + ((size_t)t * a.nsplit * H + h) * (D + 2u);
+            const bool live = lane < a.nsplit;
+            const float ls = live ? __ldcg(base + lane * stride + D + 1u) : 0.0f;
+            const float ms = (live && ls > 0.0f) ? __ldcg(base + lane * stride + D) : -INFINITY;
+            float M = ms;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+            const float w = ls > 0.0f ? expf(ms - M) : 0.0f;
+            const float Lsum = warp_sum(w * ls);
+            float acc[VCH];
+#pragma unroll
+            for (int c = 0; c < VCH; c++) acc[c] = 0.0f;
+            for (uint32_t sp = 0; sp < a.nsplit; sp++) {
+                const float ws = __shfl_sync(0xffffffffu, w, sp);
+                if (ws == 0.0f) continue;          // a split without keys wrote nothing of weight (uniform over the warp)
+#pragma unroll
+                for (int c = 0; c < VCH; c++) { const uint32_t r = lane + 32u * c; if (r < D) acc[c] = fmaf(ws, __ldcg(base + sp * stride + r), acc[c]); }
+            }
+            const float inv = 1.0f / Lsum;
 #pragma unroll
             for (int c = 0; c < VCH; c++) {
                 const uint32_t r = lane + 32u * c;
                 if (r >= D) continue;
-                float v = o[hs][qi][c] * inv;
+                float v = acc[c] * inv;
                 if (a.gate) v *= sigmoidf_(a.gate[t * a.ldg + h * D + r]);
                 a.out[t * HD + h * D + r] = v;
             }
@@ -390,6 +486,64 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
     if (live)
 #pragma unroll
         for (int k = 0; k < 4; k++) { const uint32_t n = g + LG * k; if (n < a.N) a.S[(size_t)c * a.N + n] = S[k]; }
+}
+
+// The same scan for long portions, parallel over time: blockDim = (32, segments).  A thread first composes its time segment's
+// affine map S -> P S + Q per state (P = exp of the summed exponents), the segment-0 threads chain the maps to every segment's entry
+// state (and the portion's final state), then each thread replays its segment from its entry state and writes the outputs.
+template <int LG>
+__global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a) {
+    pdl_enter();
+    __shared__ float P[32][32][4], Q[32][32][4];
+    const uint32_t x = threadIdx.x, seg = threadIdx.y, nseg = blockDim.y, gid = blockIdx.x * 32u + x, c = gid / LG, g = gid % LG;
+    const uint32_t Ls = (a.T + nseg - 1u) / nseg, t0 = min(a.T, seg * Ls), t1 = min(a.T, t0 + Ls);
+    const bool live = c < a.C;
+    float Av[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) { const uint32_t n = g + LG * k; Av[k] = (live && n < a.N) ? a.A[(size_t)c * a.N + n] : 0.0f; }
+    {
+        float zs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t t = t0; t < t1; t++) {
+            const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, dx = live ? dtc * a.x[(size_t)t * a.C + c] : 0.0f;
+            const float *row = a.bc + (size_t)t * a.ldb;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t n = g + LG * k;
+                if (n < a.N) { const float z = dtc * Av[k]; q[k] = decay_drive(z, q[k], dx * row[a.b0 + n]); zs[k] += z; }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) { P[seg][x][k] = expf(zs[k]); Q[seg][x][k] = q[k]; }
+    }
+    __syncthreads();
+    if (seg == 0 && live) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t n = g + LG * k;
+            if (n >= a.N) continue;
+            float s = a.S[(size_t)c * a.N + n];
+            for (uint32_t sg = 0; sg < nseg; sg++) { const float pg = P[sg][x][k], qg = Q[sg][x][k]; P[sg][x][k] = s; s = fmaf(pg, s, qg); }
+            a.S[(size_t)c * a.N + n] = s;
+        }
+    }
+    __syncthreads();
+    float S[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) S[k] = (live && g + LG * k < a.N) ? P[seg][x][k] : 0.0f;
+    const float Dc = live ? a.Dv[c] : 0.0f;
+    for (uint32_t t = t0; t < t1; t++) {
+        const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
+        const float *row = a.bc + (size_t)t * a.ldb;
+        float acc = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t n = g + LG * k;
+            if (n < a.N) { S[k] = decay_drive(dtc * Av[k], S[k], dx * row[a.b0 + n]); acc = fmaf(S[k], row[a.c0 + n], acc); }
+        }
+#pragma unroll
+        for (int off = LG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (live && g == 0) a.y[(size_t)t * a.C + c] = (acc + Dc * xv) * siluf_(a.z[(size_t)t * a.ldz + c]);
+    }
 }
 
 // PolyNorm over a token's feed-forward vector, in place: a N(z) + b N(z^2) + c N(z^3) + e with powers taken element by element

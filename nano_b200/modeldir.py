@@ -127,6 +127,8 @@ def rakarax_config(vocab: int, width: int, layers, max_positions: int = 512, eps
         kind, mixer, ff = ent[:3]
         L = {"type": kind, "mixer": json.loads(json.dumps(mixer)), "mlp": {"kind": "dense", "ff": ff} if ff else None}
         if len(ent) > 3 and ent[3] is not None:
+            src = {k: v for k, v in out[int(ent[3])].items() if k != "weights_of"}
+            assert src == L, "a layer with weights_of repeats the entry of the layer it names"
             L["weights_of"] = int(ent[3])
         out.append(L)
     return {"architecture": "Rakarax", "vocab": vocab, "width": width, "max_positions": max_positions, "norm": {"eps": eps}, "layers": out}

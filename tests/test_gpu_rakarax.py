@@ -218,6 +218,19 @@ def test_window_edge_shows(tmp_path, window):
     eng.close()
 
 
+@pytest.mark.parametrize("window", [150, None])
+def test_wide_window_decoding_splits_keys(tmp_path, window):
+    """Short portions deal a wide window's key pages out to several blocks and merge: same logits as the whole prompt."""
+    mixer = par({"heads": 3, "kv_heads": 1, "dim": 24, "vdim": 24, "conv": 2, "scale": 0.8, "mask": {"size": window} if window else None}, ls=1.0, rs=0.3)
+    cfg = md.rakarax_config(40, 48, [("parallel", mixer, 24), ("parallel", mixer, 24, 0)], max_positions=400)
+    eng, w = build(tmp_path, cfg, max_tokens=400)
+    t = toks(cfg, 330, seed=6)
+    ref = oracle_forward(cfg, w, t, np.float64)
+    assert rel(whole(eng, t), ref) < F32_TOL
+    assert rel(in_cuts(eng, t, [140] + [1] * 60 + [2, 3, 4, 1] * 13), ref) < F32_TOL
+    eng.close()
+
+
 def test_far_tokens_through_the_states(tmp_path):
     """A slow decay and a slow scan carry the first tokens over hundreds of positions: changing token 0 changes the last logits."""
     ret = {"heads": 2, "dim": 16, "vdim": 16, "decay": [0.9999, 1.0], "rot": {"dims": 16, "base": 1e4}}
