@@ -77,7 +77,7 @@ struct Layer {
     float *a_conv = nullptr, *temp = nullptr, *talk = nullptr, *slopes = nullptr;
     uint32_t mC = 0, mN = 0, mR = 0, m_taps = 0;
     float *m_conv = nullptr, *m_conv_b = nullptr, *dt_b = nullptr, *A = nullptr, *Dv = nullptr;
-    Weight xw, dtw, mo;
+    Weight xw, dtw, mo; float *dt_wf = nullptr;      // dt_wf: the step-size projection once more in fp32, for the scan that makes dt itself
     // feed-forward
     int ff_kind = FF_NONE; float *act = nullptr;
     bool has_mlp = false, has_shared = false;
@@ -112,11 +112,11 @@ struct LayeredEngine : nb::EngineBase {
     float *state = nullptr, *state_bak = nullptr; uint32_t *table = nullptr;
     std::vector<uint32_t> free_pages; std::vector<Seq> seqs;
     // scratch (chunk_cap tokens)
-    float *x = nullptr, *x0 = nullptr, *hm = nullptr, *h2 = nullptr, *d = nullptr;
+    float *x = nullptr, *x0 = nullptr, *hm = nullptr, *h2 = nullptr, *d = nullptr, *d2 = nullptr;
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
     float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
-    float *b_wpart = nullptr; uint32_t *b_wtick = nullptr;      // window attention: partials and tickets of the key splits
+    float *b_wpart = nullptr; uint32_t *b_wtick = nullptr, *b_rtick = nullptr;      // window attention: partials and tickets of the key splits
     float *b_p = nullptr, *b_qk = nullptr, *b_xc = nullptr, *b_a = nullptr, *b_ro = nullptr, *b_dbc = nullptr, *b_dt = nullptr, *b_y = nullptr, *b_f = nullptr;   // retention, window attention + selective scan, dense feed-forward
     uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
@@ -369,7 +369,7 @@ int load_window_ssm(Loader &ld, const nb::Json *m, const std::string &p, Layer *
     if ((r = ld.put_f32(sl, &L->slopes))) return r;
     if ((r = ld.vec(p + "right.conv", {C, L->m_taps}, &L->m_conv)) || (r = ld.vec(p + "right.conv.b", {C}, &L->m_conv_b)) || (r = ld.vec(p + "right.dt.b", {C}, &L->dt_b)) ||
         (r = ld.vec(p + "right.D", {C}, &L->Dv)) || (r = ld.stacked({p + "right.x"}, {R + 2 * N}, C, &L->xw)) || (r = ld.stacked({p + "right.dt"}, {C}, R, &L->dtw)) ||
-        (r = ld.stacked({p + "right.o"}, {E}, C, &L->mo))) return r;
+        (r = ld.stacked({p + "right.o"}, {E}, C, &L->mo)) || (r = ld.vec(p + "right.dt", {C, R}, &L->dt_wf))) return r;
     std::vector<float> al; std::vector<uint64_t> sh;
     if ((r = ld.host_f32(p + "right.A_log", &al, &sh)) || (r = ld.expect(p + "right.A_log", sh, {C, N}))) return r;
     for (float &v : al) v = (float)-exp((double)v);          // A = -exp(A_log)
@@ -412,6 +412,10 @@ int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32
     if (maxM <= kGemvMaxM) {
         a.round_a = f32 ? 0u : 1u;
         const uint32_t gx = gemv_blocks(e, a.N, active ? std::min(active, groups) : groups);
+        if (a.epi == EPI_CONV_RANGES)
+            return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 1>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 1>, dim3(gx, groups), dim3(256), 0, a);
+        if (a.a_poly)
+            return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 2>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 2>, dim3(gx, groups), dim3(256), 0, a);
         return f32 ? launch<GemmArgs>(e, k_gemv<float>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv<__nv_bfloat16>, dim3(gx, groups), dim3(256), 0, a);
     }
     const dim3 grid((a.N + 63u) / 64u, (maxM + 63u) / 64u, groups);
@@ -524,23 +528,26 @@ int mix_latent_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx 
     return 0;
 }
 
-// retention: [q | k | v | g] in one product, rotary positions on q and k (k scaled by dim^-1/2 afterwards), the recurrence over the
-// fp32 state of the slot, per-head unit RMS times silu(g), output product
+// retention: [q | k | v | g] in one product; the scan rotates q and k while it stages them (k scaled by dim^-1/2 afterwards) and runs
+// the recurrence over the fp32 state of the slot; per-head unit RMS times silu(g); output product
 int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
     const uint32_t E = e->E, T = cx.T, H = L.H, D = L.dim, VD = L.vdim, P = 2 * H * D + 2 * H * VD;
     int r;
     if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T), 1, T))) return r;
-    RopeArgs ra{e->b_p, P, 0, H * D, T, H, D, L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr};
-    if ((r = launch<RopeArgs>(e, k_rope, dim3(ew_grid((size_t)T * H * (D - L.rot_dims / 2u))), dim3(256), 0, ra))) return r;
-    RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD};
+    const bool small = T <= kGemvMaxM;      // short portions: the last block of a head also norms and gates its output
+    RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD,
+                     L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr,
+                     small ? 1u : 0u, e->b_p + 2 * H * D + H * VD, P, e->b_a, e->eps, e->b_rtick};
     const dim3 grid((VD + kRetCols - 1u) / kRetCols, H), block(256);
     if (D <= 32) r = launch<RetentionArgs>(e, k_retention_scan<1>, grid, block, 0, sa);
     else if (D <= 64) r = launch<RetentionArgs>(e, k_retention_scan<2>, grid, block, 0, sa);
     else if (D <= 128) r = launch<RetentionArgs>(e, k_retention_scan<4>, grid, block, 0, sa);
     else r = launch<RetentionArgs>(e, k_retention_scan<8>, grid, block, 0, sa);
     if (r) return r;
-    RetOutArgs oa{e->b_ro, e->b_p + 2 * H * D + H * VD, P, e->b_a, T, H, VD, e->eps};
-    if ((r = launch<RetOutArgs>(e, k_retention_out, dim3((T * H + 7u) / 8u), dim3(256), 0, oa))) return r;
+    if (!small) {
+        RetOutArgs oa{e->b_ro, e->b_p + 2 * H * D + H * VD, P, e->b_a, T, H, VD, e->eps};
+        if ((r = launch<RetOutArgs>(e, k_retention_out, dim3((T * H + 7u) / 8u), dim3(256), 0, oa))) return r;
+    }
     return gemm(e, plain(e->b_a, H * VD, L.o, e->d, E, T), 1, T);
 }
 
@@ -601,23 +608,21 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
     const uint32_t E = e->E, T = cx.T, H = L.H, G = L.G, D = L.dim, C = L.mC, N = L.mN, R = L.mR;
     const uint32_t QK = H * D + G * D, P = QK + C + H * D + C, g0 = QK + C, z0 = g0 + H * D;
     int r;
-    if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T), 1, T))) return r;
-    if ((r = conv_launch(e, ConvArgs{e->b_p, P, L.a_conv, nullptr, cx.st + run.st_conv, e->b_qk, T, QK, L.a_taps, QK, 0}))) return r;
-    if ((r = conv_launch(e, ConvArgs{e->b_p + QK, P, L.m_conv, L.m_conv_b, cx.st + run.st_conv2, e->b_xc, T, C, L.m_taps, C, 1}))) return r;
-    // left
-    QkPrepArgs qa{e->b_qk, QK, e->b_qk + H * D, QK, L.temp, L.scale, run.cache, cx.table, H, G, D, L.RL, cx.pos0, e->eps, cx.pos_ptr};
-    if ((r = launch<QkPrepArgs>(e, k_qk_prepare, dim3(T), dim3(256), 0, qa))) return r;
-    WinAttnArgs wa{e->b_qk, QK, run.cache, cx.table, e->b_p + g0, P, L.talk, L.slopes, e->b_a, T, H, G, D, L.RL, cx.pos0, L.window, L.softcap, cx.pos_ptr, 1u, e->b_wpart, e->b_wtick};
-    if (T <= kGemvMaxM) {      // short portions: the key pages of the window are dealt out to several blocks (two pages each at least)
-        const uint32_t reach = cx.pos_ptr ? e->max_tokens : cx.pos0 + T;      // a captured step does not know the position: the most pages a window can span
-        const uint32_t pages = std::min(reach, L.window + T) / kPage + 1u;
-        wa.nsplit = std::max(1u, std::min(kSplitMax, pages / 2u));
-    }
-    if ((r = win_attn_launch(e, L, wa))) return r;
+    const bool small = T <= kGemvMaxM;
+    if (small) {      // both convolutions are epilogues of the product (a warp owns a channel and its tail)
+        GemmArgs pj = plain(e->hm, E, L.proj, e->b_p, P, T, nullptr, EPI_CONV_RANGES);
+        pj.cr[0] = {0, QK, L.a_conv, nullptr, cx.st + run.st_conv, e->b_qk, L.a_taps, 0};
+        pj.cr[1] = {QK, QK + C, L.m_conv, L.m_conv_b, cx.st + run.st_conv2, e->b_xc, L.m_taps, 1};
+        if ((r = gemm(e, pj, 1, T))) return r;
+    } else if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T), 1, T))) return r;
+    // the two sides share nothing after the product: the scan side runs on a second stream and joins before the residual update
+    if (e->branch_streams) { CK(cudaEventRecord(e->ev_fork, e->stream)); e->cur = e->side; CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0)); }
     // right
+    if (!small && (r = conv_launch(e, ConvArgs{e->b_p + QK, P, L.m_conv, L.m_conv_b, cx.st + run.st_conv2, e->b_xc, T, C, L.m_taps, C, 1}))) return r;
     if ((r = gemm(e, plain(e->b_xc, C, L.xw, e->b_dbc, R + 2 * N, T), 1, T))) return r;
-    if ((r = gemm(e, plain(e->b_dbc, R + 2 * N, L.dtw, e->b_dt, C, T, L.dt_b, EPI_SOFTPLUS), 1, T))) return r;
-    SelScanArgs sa{e->b_dt, e->b_xc, e->b_dbc, R + 2 * N, R, R + N, L.A, L.Dv, e->b_p + z0, P, cx.st + run.st_S, e->b_y, T, C, N};
+    if (!small && (r = gemm(e, plain(e->b_dbc, R + 2 * N, L.dtw, e->b_dt, C, T, L.dt_b, EPI_SOFTPLUS), 1, T))) return r;
+    SelScanArgs sa{e->b_dt, e->b_xc, e->b_dbc, R + 2 * N, R, R + N, L.A, L.Dv, e->b_p + z0, P, cx.st + run.st_S, e->b_y, T, C, N,
+                   small ? L.dt_wf : nullptr, L.dt_b, R, e->f32 ? 0u : 1u};
     if (N <= 4) r = sel_scan_launch<1>(e, sa);
     else if (N <= 8) r = sel_scan_launch<2>(e, sa);
     else if (N <= 16) r = sel_scan_launch<4>(e, sa);
@@ -625,10 +630,26 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
     else if (N <= 64) r = sel_scan_launch<16>(e, sa);
     else r = sel_scan_launch<32>(e, sa);
     if (r) return r;
-    GemmArgs lo = plain(e->b_a, H * D, L.o, e->d, E, T), ro = plain(e->b_y, C, L.mo, e->d, E, T);
-    lo.c_scale = L.left_scale; lo.c_mode = C_SCALE; ro.c_scale = L.right_scale; ro.c_mode = C_SCALE | C_ADD;
+    GemmArgs ro = plain(e->b_y, C, L.mo, e->d2, E, T);
+    ro.c_scale = L.right_scale; ro.c_mode = C_SCALE;
+    if ((r = gemm(e, ro, 1, T))) return r;
+    if (e->branch_streams) { CK(cudaEventRecord(e->ev_join, e->side)); e->cur = e->stream; }
+    // left
+    if (!small && (r = conv_launch(e, ConvArgs{e->b_p, P, L.a_conv, nullptr, cx.st + run.st_conv, e->b_qk, T, QK, L.a_taps, QK, 0}))) return r;
+    QkPrepArgs qa{e->b_qk, QK, e->b_qk + H * D, QK, L.temp, L.scale, run.cache, cx.table, H, G, D, L.RL, cx.pos0, e->eps, cx.pos_ptr};
+    if ((r = launch<QkPrepArgs>(e, k_qk_prepare, dim3(T), dim3(256), 0, qa))) return r;
+    WinAttnArgs wa{e->b_qk, QK, run.cache, cx.table, e->b_p + g0, P, L.talk, L.slopes, e->b_a, T, H, G, D, L.RL, cx.pos0, L.window, L.softcap, cx.pos_ptr, 1u, e->b_wpart, e->b_wtick};
+    if (small) {      // short portions: the key pages of the window are dealt out to several blocks (two pages each at least)
+        const uint32_t reach = cx.pos_ptr ? e->max_tokens : cx.pos0 + T;      // a captured step does not know the position: the most pages a window can span
+        const uint32_t pages = std::min(reach, L.window + T) / kPage + 1u;
+        wa.nsplit = std::max(1u, std::min(kSplitMax, pages / 2u));
+    }
+    if ((r = win_attn_launch(e, L, wa))) return r;
+    GemmArgs lo = plain(e->b_a, H * D, L.o, e->d, E, T);
+    lo.c_scale = L.left_scale; lo.c_mode = C_SCALE;
     if ((r = gemm(e, lo, 1, T))) return r;
-    return gemm(e, ro, 1, T);
+    if (e->branch_streams) CK(cudaStreamWaitEvent(e->stream, e->ev_join, 0));
+    return 0;
 }
 
 int mix(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
@@ -644,13 +665,18 @@ int mix(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
 int ff_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
     int r;
     if ((r = gemm(e, plain(e->h2, e->E, L.up, e->b_f, L.ff, T), 1, T))) return r;
+    if (T <= kGemvMaxM) {      // short portions: the activation is the prologue of the second product
+        GemmArgs dn = plain(e->b_f, L.ff, L.down, e->d, e->E, T);
+        dn.a_poly = L.act; dn.a_eps = e->eps;
+        return gemm(e, dn, 1, T);
+    }
     PolyArgs pa{e->b_f, L.ff, L.act, T, L.ff, e->eps};
     if ((r = launch<PolyArgs>(e, k_polynorm, dim3(T), dim3(256), 0, pa))) return r;
     return gemm(e, plain(e->b_f, L.ff, L.down, e->d, e->E, T), 1, T);
 }
 
-int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T) {
-    SandwichArgs a{e->x, d, w_post, w_pre, out, keep, T, e->E, e->eps};
+int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T, const float *d2 = nullptr) {
+    SandwichArgs a{e->x, d, w_post, w_pre, out, keep, T, e->E, e->eps, d2};
     return launch<SandwichArgs>(e, k_sandwich, dim3(T), dim3(256), 0, a);
 }
 
@@ -672,10 +698,11 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
             const float *next_n1 = ri + 1 < e->runs.size() ? e->layers[e->runs[ri + 1].layer].n1 : nullptr;
             if (ri == 0 && (r = sandwich(e, nullptr, nullptr, L.n1, e->hm, nullptr, T))) return r;
             if ((r = mix(e, L, run, cx))) return r;
+            const float *d2 = L.type == MIX_WINDOW_SSM ? e->d2 : nullptr;      // the scan side of a two-sided mixer
             if (L.has_mlp) {
-                if ((r = sandwich(e, e->d, L.n1b, L.n2, e->h2, nullptr, T)) || (r = ff_dense(e, L, T)) ||
+                if ((r = sandwich(e, e->d, L.n1b, L.n2, e->h2, nullptr, T, d2)) || (r = ff_dense(e, L, T)) ||
                     (r = sandwich(e, e->d, L.n2b, next_n1, next_n1 ? e->hm : nullptr, keep, T))) return r;
-            } else if ((r = sandwich(e, e->d, L.n1b, next_n1, next_n1 ? e->hm : nullptr, keep, T))) return r;
+            } else if ((r = sandwich(e, e->d, L.n1b, next_n1, next_n1 ? e->hm : nullptr, keep, T, d2))) return r;
             continue;
         }
         if (run.add_embed) { k_add<<<ew_grid((size_t)T * E), 256, 0, e->stream>>>(e->x, e->x0, (size_t)T * E); CK(cudaGetLastError()); e->launches++; }
@@ -1238,6 +1265,13 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     if (win_smem[2] > 48 * 1024 && (r = win_attn_optin_v<4>((int)win_smem[2]))) return r;
     if (win_smem[3] > 48 * 1024 && (r = win_attn_optin_v<8>((int)win_smem[3]))) return r;
     if (sP) DM(e->b_p, T * sP * 4);
+    if (sQK) DM(e->d2, T * E * 4);
+    if (sRO) {
+        uint32_t mH = 0;
+        for (const Run &q : e->runs) { const Layer &L = e->layers[q.layer]; if (L.type == MIX_RETENTION) mH = std::max(mH, L.H); }
+        DM(e->b_rtick, (size_t)mH * 4);
+        CK(cudaMemset(e->b_rtick, 0, (size_t)mH * 4));
+    }
     if (sQK) {
         uint32_t mPart = 0;
         for (const Run &q : e->runs) { const Layer &L = e->layers[q.layer]; if (L.type == MIX_WINDOW_SSM) mPart = std::max(mPart, L.H * (L.dim + 2)); }

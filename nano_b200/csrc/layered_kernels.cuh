@@ -37,7 +37,7 @@ constexpr uint32_t kAttnWarps = 8;        // heads per attention block
 constexpr uint32_t kGemvMaxM = 4;         // rows a k_gemv launch handles per group
 
 enum CMode : uint32_t { C_ADD = 1, C_SCALE = 2 };
-enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5, EPI_SOFTPLUS = 6 };
+enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5, EPI_SOFTPLUS = 6, EPI_CONV_RANGES = 7 };
 
 // C[r, c0 + n] = epi( sum_k A[arow(r), a0 + k] * W[g][n, k] + bias[g][n] )   for the rows r of group g
 //   rows of group g : [g_off[g], g_off[g+1])  when g_off is given (sizes known on the device only), else [0, M)
@@ -60,6 +60,12 @@ struct GemmArgs {
     // After the epilogue: with c_mode & C_SCALE the value is multiplied by c_scale, with c_mode & C_ADD it is added to what C holds,
     // so two products can be summed with fixed weights into one output (C = s1 A1 W1^T, then C += s2 A2 W2^T).
     float c_scale; uint32_t c_mode;
+    // k_gemv only.  Prologue: when a_poly is given (4 numbers a, b, c, e), row r of A is used as a N(z) + b N(z^2) + c N(z^3) + e with
+    // z = A[r, 0..K), powers element by element and N(u) = u / sqrt(mean(u^2) + a_eps).
+    const float *a_poly;
+    // k_gemv only.  Epilogue EPI_CONV_RANGES: a column n inside [cr[i].n0, cr[i].n1) is channel n - n0 of causal convolution i over the
+    // rows in order (no epilogue before it); every other column is stored as usual.
+    struct ConvRange { uint32_t n0, n1; const float *taps, *bias; float *state, *out; uint32_t K, act; } cr[2];
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -319,11 +325,33 @@ __device__ __forceinline__ void conv_rows(const GemmArgs &a, uint32_t c, uint32_
     }
 }
 
+// EPI_CONV_RANGES for channel c of range r: taps [C][K], bias optional, tail [K - 1][C], out [rows][C], silu when r.act
+__device__ __forceinline__ void conv_range_rows(const GemmArgs::ConvRange &r, uint32_t c, const float (&v)[kGemvMaxM], uint32_t rows, uint32_t r0) {
+    const uint32_t K = r.K, C = r.n1 - r.n0;
+    for (uint32_t t = 0; t < rows; t++) {
+        float s = r.bias ? r.bias[c] : 0.0f;
+        for (uint32_t j = 0; j < K; j++) {
+            const int32_t src = (int32_t)t - (int32_t)(K - 1u - j);
+            const float x = src >= 0 ? pick_row(v, src) : r.state[(size_t)((int32_t)(K - 1u) + src) * C + c];
+            s = fmaf(r.taps[(size_t)c * K + j], x, s);
+        }
+        if (r.act) s = s / (1.0f + expf(-s));
+        r.out[(size_t)(r0 + t) * C + c] = s;
+    }
+    for (uint32_t j = 0; j + 1u < K; j++) {
+        const int32_t src = (int32_t)rows - (int32_t)(K - 1u) + (int32_t)j;
+        r.state[(size_t)j * C + c] = src >= 0 ? pick_row(v, src) : r.state[(size_t)(j + rows) * C + c];
+    }
+}
+
 // dot products of one weight row with up to kGemvMaxM activation rows, summed over the warp's lanes: every lane returns the totals.
-// sc[i] / nw: the optional RMS-norm prologue (A[i][k] * sc[i] * nw[k]); rnd: round the activation to bf16 first.
-template <typename WT>
+// sc[i] / nw: the optional RMS-norm prologue (A[i][k] * sc[i] * nw[k]); pc: the optional PolyNorm prologue, pc[i] = (a / rms(z), b / rms(z^2),
+// c / rms(z^3), e) of row i; rnd: round the activation to bf16 first.
+struct PolyRow { float r1, r2, r3, e; };
+__device__ __forceinline__ float poly_of(float x, const PolyRow &p) { return fmaf(p.r1, x, fmaf(p.r2, x * x, fmaf(p.r3, x * x * x, p.e))); }
+template <typename WT, bool POLY = false>
 __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemvMaxM], uint32_t rows, uint32_t K, uint32_t kvec, const float (&sc)[kGemvMaxM],
-                                          const float *nw, bool rnd, uint32_t lane, float (&acc)[kGemvMaxM]) {
+                                          const float *nw, bool rnd, uint32_t lane, float (&acc)[kGemvMaxM], const PolyRow *pc = nullptr) {
     constexpr uint32_t VN = WVec<WT>::N;
 #pragma unroll
     for (uint32_t i = 0; i < kGemvMaxM; i++) acc[i] = 0.0f;
@@ -338,6 +366,7 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
                 for (uint32_t j = 0; j < VN; j += 4) {
                     float4 x = *reinterpret_cast<const float4 *>(ap[i] + k + j);
                     if (nw) { const float4 g = __ldg(reinterpret_cast<const float4 *>(nw + k + j)); x.x = x.x * sc[i] * g.x; x.y = x.y * sc[i] * g.y; x.z = x.z * sc[i] * g.z; x.w = x.w * sc[i] * g.w; }
+                    if (POLY && pc) { x.x = poly_of(x.x, pc[i]); x.y = poly_of(x.y, pc[i]); x.z = poly_of(x.z, pc[i]); x.w = poly_of(x.w, pc[i]); }
                     if (rnd) { x.x = round_bf16(x.x); x.y = round_bf16(x.y); x.z = round_bf16(x.z); x.w = round_bf16(x.w); }
                     acc[i] = fmaf(w[j], x.x, acc[i]); acc[i] = fmaf(w[j + 1], x.y, acc[i]);
                     acc[i] = fmaf(w[j + 2], x.z, acc[i]); acc[i] = fmaf(w[j + 3], x.w, acc[i]);
@@ -352,6 +381,7 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
             if (i < rows) {
                 float x = ap[i][k];
                 if (nw) x = x * sc[i] * nw[k];
+                if (POLY && pc) x = poly_of(x, pc[i]);
                 acc[i] = fmaf(w, rnd ? round_bf16(x) : x, acc[i]);
             }
     }
@@ -361,7 +391,8 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
         for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
 }
 
-template <typename WT>
+// EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue (registers the plain one keeps)
+template <typename WT, int EXT = 0>
 __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const GroupView gv = group_view(a, blockIdx.y);
     if (gv.rows == 0) return;
@@ -389,11 +420,30 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
                 sc[i] = 1.0f / sqrtf(s / (float)a.K + a.a_eps);
             }
     }
+    PolyRow pc[EXT == 2 ? kGemvMaxM : 1];
+    if (EXT == 2 && a.a_poly) {
+#pragma unroll
+        for (uint32_t i = 0; i < kGemvMaxM; i++)
+            if (i < rows) {
+                float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+                for (uint32_t k = threadIdx.x; k < a.K; k += blockDim.x) { const float v = ap[i][k], v2 = v * v, v3 = v2 * v; s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6); }
+                s2 = block_sum(s2, red); s4 = block_sum(s4, red); s6 = block_sum(s6, red);
+                pc[i].r1 = a.a_poly[0] / sqrtf(s2 / (float)a.K + a.a_eps); pc[i].r2 = a.a_poly[1] / sqrtf(s4 / (float)a.K + a.a_eps);
+                pc[i].r3 = a.a_poly[2] / sqrtf(s6 / (float)a.K + a.a_eps); pc[i].e = a.a_poly[3];
+            }
+    }
     const uint32_t kvec = vec ? (a.K / WVec<WT>::N) * WVec<WT>::N : 0u;
     for (uint32_t n = warp0; n < a.N; n += nwarps) {
         float acc[kGemvMaxM];
-        warp_dots<WT>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc);
+        warp_dots<WT, EXT == 2>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc, (EXT == 2 && a.a_poly) ? pc : nullptr);
         if (lane != 0) continue;
+        if (EXT == 1 && a.epi == EPI_CONV_RANGES) {
+            bool done = false;
+#pragma unroll
+            for (int ri = 0; ri < 2; ri++)
+                if (n >= a.cr[ri].n0 && n < a.cr[ri].n1) { conv_range_rows(a.cr[ri], n - a.cr[ri].n0, acc, rows, gv.r0); done = true; }
+            if (done) continue;
+        }
         if (a.epi == EPI_GELU_CONV && n >= a.split) {
             float v[kGemvMaxM];
 #pragma unroll
@@ -422,6 +472,14 @@ __global__ void __launch_bounds__(256) k_gemv(const GemmArgs a) {
     pdl_wait();
     __shared__ float red[32];
     gemv_body<WT>(a, red);
+}
+template <typename WT, int EXT>
+__global__ void __launch_bounds__(256) k_gemv_ext(const GemmArgs a) {
+    pdl_launch_next();
+    gemv_prefetch<WT>(a);
+    pdl_wait();
+    __shared__ float red[32];
+    gemv_body<WT, EXT>(a, red);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -42,20 +42,21 @@ __global__ void k_embed_pos(const uint32_t *__restrict__ tokens, const uint32_t 
 
 // One token per block.  With d: x[t] += d[t] / rms(d[t]) * (1 + w_post) (the sublayer's output norm and the residual sum); keep
 // (optional) receives the updated x; with out: out[t] = x[t] / rms(x[t]) * (1 + w_pre), the input of the sublayer that follows.
-struct SandwichArgs { float *x; const float *d; const float *w_post, *w_pre; float *out; float *keep; uint32_t T, E; float eps; };
+// d2 (optional): a second branch of the sublayer, d + d2 is what gets normed.
+struct SandwichArgs { float *x; const float *d; const float *w_post, *w_pre; float *out; float *keep; uint32_t T, E; float eps; const float *d2; };
 __global__ void __launch_bounds__(256) k_sandwich(const SandwichArgs a) {
     pdl_enter();
     __shared__ float red[32];
     const size_t row = (size_t)blockIdx.x * a.E;
     float *xt = a.x + row;
     if (a.d) {
-        const float *dt = a.d + row;
+        const float *dt = a.d + row, *d2 = a.d2 ? a.d2 + row : nullptr;
         float s = 0.0f;
-        for (uint32_t i = threadIdx.x; i < a.E; i += blockDim.x) s = fmaf(dt[i], dt[i], s);
+        for (uint32_t i = threadIdx.x; i < a.E; i += blockDim.x) { const float v = d2 ? dt[i] + d2[i] : dt[i]; s = fmaf(v, v, s); }
         s = block_sum(s, red);
         const float rinv = 1.0f / sqrtf(s / (float)a.E + a.eps);
         for (uint32_t i = threadIdx.x; i < a.E; i += blockDim.x) {
-            const float v = xt[i] + dt[i] * rinv * (1.0f + a.w_post[i]);
+            const float v = xt[i] + (d2 ? dt[i] + d2[i] : dt[i]) * rinv * (1.0f + a.w_post[i]);
             xt[i] = v;
             if (a.keep) a.keep[row + i] = v;
         }
@@ -100,7 +101,12 @@ __global__ void k_rope(const RopeArgs a) {
 // keeps S[h][:, j] in registers (lane l holds key coordinates l, l + 32, ...); per token S <- decay_h S + k v_j and o_j = S . q.
 // q, k (already rotated and scaled) and v of kRetTile tokens at a time are staged in shared memory, read there by every warp.
 // p rows hold q at q0, k at k0, v at v0.  The state is [H][VD][D] fp32; o is [T][H * VD].
-struct RetentionArgs { const float *p; uint32_t ld, q0, k0, v0; const float *decay; float *S; float *o; uint32_t T, H, D, VD; };
+// Rotary positions are applied while q and k are staged (rot_tab given: the table of k_rope; k times kscale afterwards in any case).
+// finish (short portions): the block that draws the last ticket of its head (one zeroed counter per head) also does k_retention_out's
+// work for the head: out = o / rms(o) * silu(g).
+struct RetentionArgs { const float *p; uint32_t ld, q0, k0, v0; const float *decay; float *S; float *o; uint32_t T, H, D, VD;
+                       uint32_t dims, pos0; const float2 *rot_tab; float kscale; const uint32_t *pos_ptr;
+                       uint32_t finish; const float *g; uint32_t ldg; float *out; float eps; uint32_t *tickets; };
 constexpr uint32_t kRetCpw = 4, kRetCols = 8 * kRetCpw, kRetTile = 16;
 template <int DCH>
 __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
@@ -113,14 +119,25 @@ __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
 #pragma unroll
         for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; S[i][c] = (jw + i < a.VD && d < a.D) ? a.S[((size_t)h * a.VD + jw + i) * a.D + d] : 0.0f; }
     const float g = a.decay[h];
+    const uint32_t half = a.rot_tab ? a.dims / 2u : 0u, pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
     for (uint32_t t0 = 0; t0 < a.T; t0 += kRetTile) {
         const uint32_t nt = min(kRetTile, a.T - t0);
         __syncthreads();
         for (uint32_t i = threadIdx.x; i < nt * DCH * 32u; i += blockDim.x) {
             const uint32_t t = i / (DCH * 32u), d = i % (DCH * 32u);
-            const float *row = a.p + (size_t)(t0 + t) * a.ld;
-            qs[t][d] = d < a.D ? row[a.q0 + h * a.D + d] : 0.0f;
-            ks[t][d] = d < a.D ? row[a.k0 + h * a.D + d] : 0.0f;
+            const float *qr = a.p + (size_t)(t0 + t) * a.ld + a.q0 + h * a.D, *kr = a.p + (size_t)(t0 + t) * a.ld + a.k0 + h * a.D;
+            float qv = 0.0f, kv = 0.0f;
+            if (d < a.D) {
+                qv = qr[d]; kv = kr[d];
+                if (d < 2u * half) {          // the pair (i, i + half): (u, v) -> (u cos - v sin, v cos + u sin)
+                    const bool lo = d < half;
+                    const float2 cs = a.rot_tab[(size_t)(pos + t0 + t) * half + (lo ? d : d - half)];
+                    const float qo = lo ? -qr[d + half] : qr[d - half], ko = lo ? -kr[d + half] : kr[d - half];
+                    qv = qv * cs.x + qo * cs.y; kv = kv * cs.x + ko * cs.y;
+                }
+                kv *= a.kscale;
+            }
+            qs[t][d] = qv; ks[t][d] = kv;
         }
         for (uint32_t i = threadIdx.x; i < nt * kRetCols; i += blockDim.x) {
             const uint32_t t = i / kRetCols, j = i % kRetCols;
@@ -149,6 +166,27 @@ __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
     for (uint32_t i = 0; i < kRetCpw; i++)
 #pragma unroll
         for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; if (jw + i < a.VD && d < a.D) a.S[((size_t)h * a.VD + jw + i) * a.D + d] = S[i][c]; }
+    if (!a.finish) return;
+    __shared__ uint32_t last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t got = atomicAdd(a.tickets + h, 1u);
+        last_s = got + 1u == gridDim.x;
+        if (last_s) a.tickets[h] = 0u;              // ready for the next launch
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    for (uint32_t t = warp; t < a.T; t += blockDim.x >> 5) {          // a warp per token: the head's o over all value columns
+        const float *o = a.o + ((size_t)t * a.H + h) * a.VD, *gp = a.g + (size_t)t * a.ldg + h * a.VD;
+        float s = 0.0f;
+        for (uint32_t i = lane; i < a.VD; i += 32u) { const float v = __ldcg(o + i); s = fmaf(v, v, s); }
+        s = warp_sum(s);
+        const float rinv = 1.0f / sqrtf(s / (float)a.VD + a.eps);
+        float *out = a.out + ((size_t)t * a.H + h) * a.VD;
+        for (uint32_t i = lane; i < a.VD; i += 32u) out[i] = __ldcg(o + i) * rinv * siluf_(gp[i]);
+    }
 }
 
 // each head's o divided by its root mean square over the value columns, times silu(gate): a warp per (token, head)
@@ -451,8 +489,10 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
 __device__ __forceinline__ float decay_drive(float z, float S, float b) {
     return z > -0.25f ? S + fmaf(expm1f(z), S, b) : fmaf(expf(z), S, b);
 }
+// With dt_w (fp32 [C][R], short portions) the step size is made here: dt_c = softplus(dt_w[c] . bc[t][0..R) + dt_b[c]); round_a rounds
+// that operand to bf16 first, as a tensor-core product of the same numbers would.
 struct SelScanArgs { const float *dt; const float *x; const float *bc; uint32_t ldb, b0, c0; const float *A, *Dv; const float *z; uint32_t ldz;
-                     float *S; float *y; uint32_t T, C, N; };
+                     float *S; float *y; uint32_t T, C, N; const float *dt_w, *dt_b; uint32_t R, round_a; };
 template <int LG>
 __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
     pdl_enter();
@@ -468,8 +508,16 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
     }
     const float Dc = live ? a.Dv[c] : 0.0f;
     for (uint32_t t = 0; t < a.T; t++) {
-        const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
         const float *row = a.bc + (size_t)t * a.ldb;
+        float dtc;
+        if (a.dt_w) {          // the group's lanes share the dot product of length R
+            float s = 0.0f;
+            if (live) for (uint32_t r = g; r < a.R; r += LG) { const float v = row[r]; s = fmaf(a.dt_w[(size_t)c * a.R + r], a.round_a ? round_bf16(v) : v, s); }
+#pragma unroll
+            for (int off = LG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            dtc = live ? softplusf_(s + a.dt_b[c]) : 0.0f;
+        } else dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f;
+        const float xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
         float acc = 0.0f;
 #pragma unroll
         for (int k = 0; k < 4; k++) {
