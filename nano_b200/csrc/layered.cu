@@ -538,11 +538,15 @@ int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
     RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD,
                      L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr,
                      small ? 1u : 0u, e->b_p + 2 * H * D + H * VD, P, e->b_a, e->eps, e->b_rtick};
-    const dim3 grid((VD + kRetCols - 1u) / kRetCols, H), block(256);
-    if (D <= 32) r = launch<RetentionArgs>(e, k_retention_scan<1>, grid, block, 0, sa);
-    else if (D <= 64) r = launch<RetentionArgs>(e, k_retention_scan<2>, grid, block, 0, sa);
-    else if (D <= 128) r = launch<RetentionArgs>(e, k_retention_scan<4>, grid, block, 0, sa);
-    else r = launch<RetentionArgs>(e, k_retention_scan<8>, grid, block, 0, sa);
+    // columns per warp: four where that still gives every SM a dozen warps, else one
+    const uint32_t cpw = (size_t)H * VD / 4u >= (size_t)e->num_sms * 12u ? 4u : 1u;
+    const dim3 grid((VD + 8u * cpw - 1u) / (8u * cpw), H), block(256);
+#define RET_LAUNCH(DCH) (cpw == 4 ? launch<RetentionArgs>(e, k_retention_scan<DCH, 4>, grid, block, 0, sa) : launch<RetentionArgs>(e, k_retention_scan<DCH, 1>, grid, block, 0, sa))
+    if (D <= 32) r = RET_LAUNCH(1);
+    else if (D <= 64) r = RET_LAUNCH(2);
+    else if (D <= 128) r = RET_LAUNCH(4);
+    else r = RET_LAUNCH(8);
+#undef RET_LAUNCH
     if (r) return r;
     if (!small) {
         RetOutArgs oa{e->b_ro, e->b_p + 2 * H * D + H * VD, P, e->b_a, T, H, VD, e->eps};
@@ -677,7 +681,8 @@ int ff_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
 
 int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T, const float *d2 = nullptr) {
     SandwichArgs a{e->x, d, w_post, w_pre, out, keep, T, e->E, e->eps, d2};
-    return launch<SandwichArgs>(e, k_sandwich, dim3(T), dim3(256), 0, a);
+    // a short portion is a few lone blocks: wide ones, so that a thread's chain of loads stays short
+    return launch<SandwichArgs>(e, k_sandwich, dim3(T), dim3(T <= kGemvMaxM && e->E >= 2048 ? 1024 : (T <= kGemvMaxM && e->E >= 1024 ? 512 : 256)), 0, a);
 }
 
 // every layer run over T tokens (x already holds their embeddings) of the sequence in `slot`, whose first token sits at pos0

@@ -44,7 +44,7 @@ __global__ void k_embed_pos(const uint32_t *__restrict__ tokens, const uint32_t 
 // (optional) receives the updated x; with out: out[t] = x[t] / rms(x[t]) * (1 + w_pre), the input of the sublayer that follows.
 // d2 (optional): a second branch of the sublayer, d + d2 is what gets normed.
 struct SandwichArgs { float *x; const float *d; const float *w_post, *w_pre; float *out; float *keep; uint32_t T, E; float eps; const float *d2; };
-__global__ void __launch_bounds__(256) k_sandwich(const SandwichArgs a) {
+__global__ void __launch_bounds__(1024) k_sandwich(const SandwichArgs a) {
     pdl_enter();
     __shared__ float red[32];
     const size_t row = (size_t)blockIdx.x * a.E;
@@ -97,7 +97,7 @@ __global__ void k_rope(const RopeArgs a) {
     }
 }
 
-// Retention, token by token.  A block of 8 warps owns kRetCols value columns of head h = blockIdx.y (a warp kRetCpw of them) and
+// Retention, token by token.  A block of 8 warps owns 8 x CPW value columns of head h = blockIdx.y (a warp CPW of them) and
 // keeps S[h][:, j] in registers (lane l holds key coordinates l, l + 32, ...); per token S <- decay_h S + k v_j and o_j = S . q.
 // q, k (already rotated and scaled) and v of kRetTile tokens at a time are staged in shared memory, read there by every warp.
 // p rows hold q at q0, k at k0, v at v0.  The state is [H][VD][D] fp32; o is [T][H * VD].
@@ -107,10 +107,12 @@ __global__ void k_rope(const RopeArgs a) {
 struct RetentionArgs { const float *p; uint32_t ld, q0, k0, v0; const float *decay; float *S; float *o; uint32_t T, H, D, VD;
                        uint32_t dims, pos0; const float2 *rot_tab; float kscale; const uint32_t *pos_ptr;
                        uint32_t finish; const float *g; uint32_t ldg; float *out; float eps; uint32_t *tickets; };
-constexpr uint32_t kRetCpw = 4, kRetCols = 8 * kRetCpw, kRetTile = 16;
-template <int DCH>
+constexpr uint32_t kRetTile = 16;
+// CPW: value columns per warp (4: fewest shared-memory reads per FMA; 1: most warps, for models whose heads x columns would leave SMs idle)
+template <int DCH, int CPW>
 __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
     pdl_enter();
+    constexpr uint32_t kRetCpw = CPW, kRetCols = 8 * CPW;
     __shared__ float qs[kRetTile][DCH * 32], ks[kRetTile][DCH * 32], vs[kRetTile][kRetCols];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = blockIdx.y, j0 = blockIdx.x * kRetCols, jw = j0 + warp * kRetCpw;
     float S[kRetCpw][DCH];
@@ -487,7 +489,11 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
 // place of a number near 1) would be several times the rounding of the sum itself; for small |z| the decay is taken as 1 + expm1(z),
 // whose error is relative to |z|, and applied as S + (expm1(z) S + b).
 __device__ __forceinline__ float decay_drive(float z, float S, float b) {
-    return z > -0.25f ? S + fmaf(expm1f(z), S, b) : fmaf(expf(z), S, b);
+    if (z > -0.25f) {          // expm1(z) by its series to z^7 / 7!: the first term left out is below 2e-9 |z| here
+        const float p = fmaf(z, fmaf(z, fmaf(z, fmaf(z, fmaf(z, fmaf(z, 1.0f / 5040.0f, 1.0f / 720.0f), 1.0f / 120.0f), 1.0f / 24.0f), 1.0f / 6.0f), 0.5f), 1.0f);
+        return S + fmaf(z * p, S, b);
+    }
+    return fmaf(expf(z), S, b);
 }
 // With dt_w (fp32 [C][R], short portions) the step size is made here: dt_c = softplus(dt_w[c] . bc[t][0..R) + dt_b[c]); round_a rounds
 // that operand to bf16 first, as a tensor-core product of the same numbers would.
