@@ -93,6 +93,7 @@ struct Seq { bool live = false; uint32_t len = 0; std::vector<uint32_t> pages; }
 constexpr float kRglruDecay = 8.0f;      // a = exp(-8 r softplus(lam)): fixed by the design
 constexpr uint32_t kWantBatch = 64;      // rows of logits computed per head product
 constexpr uint32_t kSplitMax = 32;
+constexpr uint32_t kRetSegs = 8;             // time segments of a long retention portion (k_retention_chain holds as many states in registers)
 constexpr uint32_t kNoWindow = 1u << 30;      // window of an attention without a mask: every earlier key is seen
 
 }  // namespace
@@ -116,7 +117,7 @@ struct LayeredEngine : nb::EngineBase {
     float *b_yx = nullptr, *b_u = nullptr, *b_g = nullptr, *b_sy = nullptr;                          // recurrent block
     float *b_z = nullptr, *b_cq = nullptr, *b_q = nullptr, *b_qa = nullptr, *b_ol = nullptr, *b_ov = nullptr, *b_part = nullptr;   // attention
     float *b_wt = nullptr, *b_hb = nullptr, *b_eo = nullptr, *b_sh = nullptr, *b_so = nullptr;                   // feed-forward
-    float *b_wpart = nullptr; uint32_t *b_wtick = nullptr, *b_rtick = nullptr;      // window attention: partials and tickets of the key splits
+    float *b_wpart = nullptr, *b_rseg = nullptr; uint32_t *b_wtick = nullptr, *b_rtick = nullptr;      // window attention: partials and tickets of the key splits
     float *b_p = nullptr, *b_qk = nullptr, *b_xc = nullptr, *b_a = nullptr, *b_ro = nullptr, *b_dbc = nullptr, *b_dt = nullptr, *b_y = nullptr, *b_f = nullptr;   // retention, window attention + selective scan, dense feed-forward
     uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
@@ -537,16 +538,33 @@ int mix_retention(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
     const bool small = T <= kGemvMaxM;      // short portions: the last block of a head also norms and gates its output
     RetentionArgs sa{e->b_p, P, 0, H * D, 2 * H * D, L.decay, cx.st + run.st_S, e->b_ro, T, H, D, VD,
                      L.rot_dims, cx.pos0, L.rot_tab, (float)(1.0 / sqrt((double)D)), cx.pos_ptr,
-                     small ? 1u : 0u, e->b_p + 2 * H * D + H * VD, P, e->b_a, e->eps, e->b_rtick};
-    // columns per warp: four where that still gives every SM a dozen warps, else one
-    const uint32_t cpw = (size_t)H * VD / 4u >= (size_t)e->num_sms * 12u ? 4u : 1u;
-    const dim3 grid((VD + 8u * cpw - 1u) / (8u * cpw), H), block(256);
+                     small ? 1u : 0u, e->b_p + 2 * H * D + H * VD, P, e->b_a, e->eps, e->b_rtick, 0u, 0u, e->b_rseg};
+    // long portions: time segments side by side (built states, chained, then replayed with outputs)
+    const uint32_t nseg = T >= 64 ? std::min(kRetSegs, T / 32u) : 1u;
+    if (nseg > 1) {
+        // every block of a head stages the head's q and k: rotate them once, in place, instead of in each of those blocks
+        sa.seg_len = (T + nseg - 1u) / nseg;
+        RopeArgs ra{e->b_p, P, 0, H * D, T, H, D, L.rot_dims, cx.pos0, L.rot_tab, sa.kscale, cx.pos_ptr};
+        if ((r = launch<RopeArgs>(e, k_rope, dim3(ew_grid((size_t)T * H * (D - (L.rot_tab ? L.rot_dims / 2u : 0u)))), dim3(256), 0, ra))) return r;
+        sa.rot_tab = nullptr; sa.kscale = 1.0f;
+    }
+    // columns per warp: four (fewest staged bytes per FMA) where the grid still gives every SM a dozen warps, else one
+    const uint32_t cpw = (size_t)H * VD / 4u * nseg >= (size_t)e->num_sms * 12u ? 4u : 1u;
+    const dim3 grid((VD + 8u * cpw - 1u) / (8u * cpw), H, nseg), block(256);
+    for (uint32_t pass = (nseg > 1 ? 1u : 0u); pass <= (nseg > 1 ? 2u : 0u); pass++) {
+        sa.mode = pass;
 #define RET_LAUNCH(DCH) (cpw == 4 ? launch<RetentionArgs>(e, k_retention_scan<DCH, 4>, grid, block, 0, sa) : launch<RetentionArgs>(e, k_retention_scan<DCH, 1>, grid, block, 0, sa))
-    if (D <= 32) r = RET_LAUNCH(1);
-    else if (D <= 64) r = RET_LAUNCH(2);
-    else if (D <= 128) r = RET_LAUNCH(4);
-    else r = RET_LAUNCH(8);
+        if (D <= 32) r = RET_LAUNCH(1);
+        else if (D <= 64) r = RET_LAUNCH(2);
+        else if (D <= 128) r = RET_LAUNCH(4);
+        else r = RET_LAUNCH(8);
 #undef RET_LAUNCH
+        if (r) return r;
+        if (pass == 1) {
+            RetChainArgs ca{cx.st + run.st_S, e->b_rseg, L.decay, H, D, VD, T, sa.seg_len, nseg};
+            if ((r = launch<RetChainArgs>(e, k_retention_chain, dim3((VD * D + 255u) / 256u, H), dim3(256), 0, ca))) return r;
+        }
+    }
     if (r) return r;
     if (!small) {
         RetOutArgs oa{e->b_ro, e->b_p + 2 * H * D + H * VD, P, e->b_a, T, H, VD, e->eps};
@@ -1272,8 +1290,9 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     if (sP) DM(e->b_p, T * sP * 4);
     if (sQK) DM(e->d2, T * E * 4);
     if (sRO) {
-        uint32_t mH = 0;
-        for (const Run &q : e->runs) { const Layer &L = e->layers[q.layer]; if (L.type == MIX_RETENTION) mH = std::max(mH, L.H); }
+        uint32_t mH = 0; size_t mS = 0;
+        for (const Run &q : e->runs) { const Layer &L = e->layers[q.layer]; if (L.type == MIX_RETENTION) { mH = std::max(mH, L.H); mS = std::max(mS, (size_t)L.H * L.vdim * L.dim); } }
+        DM(e->b_rseg, (size_t)kRetSegs * mS * 4);
         DM(e->b_rtick, (size_t)mH * 4);
         CK(cudaMemset(e->b_rtick, 0, (size_t)mH * 4));
     }

@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(1024) k_sandwich(const SandwichArgs a) {
 // multiplied by kscale afterwards (1: none).  buf rows hold q at column q0 and k at column k0, H heads of D each.
 struct RopeArgs { float *buf; uint32_t ld, q0, k0, T, H, D, dims, pos0; const float2 *tab; float kscale; const uint32_t *pos_ptr; };
 __device__ __forceinline__ void rope_item(const RopeArgs &a, float *q, float *k, uint32_t pos, uint32_t i) {
-    const uint32_t half = a.dims / 2u;
+    const uint32_t half = a.tab ? a.dims / 2u : 0u;
     if (i < half) {
         const float2 cs = a.tab[(size_t)pos * half + i];
         const float qu = q[i], qv = q[i + half], ku = k[i], kv = k[i + half];
@@ -88,7 +88,7 @@ __device__ __forceinline__ void rope_item(const RopeArgs &a, float *q, float *k,
 }
 __global__ void k_rope(const RopeArgs a) {
     pdl_enter();
-    const uint32_t per = a.D - a.dims / 2u, pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
+    const uint32_t per = a.D - (a.tab ? a.dims / 2u : 0u), pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
     const size_t total = (size_t)a.T * a.H * per;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(idx / ((size_t)a.H * per)), rem = (uint32_t)(idx % ((size_t)a.H * per)), h = rem / per, i = rem % per;
@@ -99,38 +99,44 @@ __global__ void k_rope(const RopeArgs a) {
 
 // Retention, token by token.  A block of 8 warps owns 8 x CPW value columns of head h = blockIdx.y (a warp CPW of them) and
 // keeps S[h][:, j] in registers (lane l holds key coordinates l, l + 32, ...); per token S <- decay_h S + k v_j and o_j = S . q.
-// q, k (already rotated and scaled) and v of kRetTile tokens at a time are staged in shared memory, read there by every warp.
+// q, k and v of 32 (or 16) tokens at a time are staged in shared memory, read there by every warp.
 // p rows hold q at q0, k at k0, v at v0.  The state is [H][VD][D] fp32; o is [T][H * VD].
 // Rotary positions are applied while q and k are staged (rot_tab given: the table of k_rope; k times kscale afterwards in any case).
 // finish (short portions): the block that draws the last ticket of its head (one zeroed counter per head) also does k_retention_out's
 // work for the head: out = o / rms(o) * silu(g).
 struct RetentionArgs { const float *p; uint32_t ld, q0, k0, v0; const float *decay; float *S; float *o; uint32_t T, H, D, VD;
                        uint32_t dims, pos0; const float2 *rot_tab; float kscale; const uint32_t *pos_ptr;
-                       uint32_t finish; const float *g; uint32_t ldg; float *out; float eps; uint32_t *tickets; };
-constexpr uint32_t kRetTile = 16;
+                       uint32_t finish; const float *g; uint32_t ldg; float *out; float eps; uint32_t *tickets;
+                       // Long portions run parallel over time: gridDim.z segments of seg_len tokens.  mode 1: every segment starts from zero
+                       // and leaves the state it builds in seg_S[segment] (no outputs); k_retention_chain turns those into the states each
+                       // segment starts from (and the slot's state after the portion); mode 2: every segment starts from seg_S[segment]
+                       // and writes its outputs (the slot's state is not touched).  mode 0: one pass over all tokens from and to S.
+                       uint32_t mode, seg_len; float *seg_S; };
 // CPW: value columns per warp (4: fewest shared-memory reads per FMA; 1: most warps, for models whose heads x columns would leave SMs idle)
 template <int DCH, int CPW>
 __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
     pdl_enter();
-    constexpr uint32_t kRetCpw = CPW, kRetCols = 8 * CPW;
+    constexpr uint32_t kRetCpw = CPW, kRetCols = 8 * CPW, kRetTile = DCH <= 4 ? 32 : 16;          // tokens staged at a time
     __shared__ float qs[kRetTile][DCH * 32], ks[kRetTile][DCH * 32], vs[kRetTile][kRetCols];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = blockIdx.y, j0 = blockIdx.x * kRetCols, jw = j0 + warp * kRetCpw;
+    float *Sio = a.mode ? a.seg_S + (size_t)blockIdx.z * a.H * a.VD * a.D : a.S;          // where this block's state comes from and goes to
+    const uint32_t t_lo = a.mode ? blockIdx.z * a.seg_len : 0u, t_hi = a.mode ? min(a.T, t_lo + a.seg_len) : a.T;
     float S[kRetCpw][DCH];
 #pragma unroll
     for (uint32_t i = 0; i < kRetCpw; i++)
 #pragma unroll
-        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; S[i][c] = (jw + i < a.VD && d < a.D) ? a.S[((size_t)h * a.VD + jw + i) * a.D + d] : 0.0f; }
+        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; S[i][c] = (a.mode != 1u && jw + i < a.VD && d < a.D) ? Sio[((size_t)h * a.VD + jw + i) * a.D + d] : 0.0f; }
     const float g = a.decay[h];
     const uint32_t half = a.rot_tab ? a.dims / 2u : 0u, pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
-    for (uint32_t t0 = 0; t0 < a.T; t0 += kRetTile) {
-        const uint32_t nt = min(kRetTile, a.T - t0);
+    for (uint32_t t0 = t_lo; t0 < t_hi; t0 += kRetTile) {
+        const uint32_t nt = min(kRetTile, t_hi - t0);
         __syncthreads();
         for (uint32_t i = threadIdx.x; i < nt * DCH * 32u; i += blockDim.x) {
             const uint32_t t = i / (DCH * 32u), d = i % (DCH * 32u);
             const float *qr = a.p + (size_t)(t0 + t) * a.ld + a.q0 + h * a.D, *kr = a.p + (size_t)(t0 + t) * a.ld + a.k0 + h * a.D;
             float qv = 0.0f, kv = 0.0f;
             if (d < a.D) {
-                qv = qr[d]; kv = kr[d];
+                qv = a.mode == 1u ? 0.0f : qr[d]; kv = kr[d];          // the state-only pass needs no q
                 if (d < 2u * half) {          // the pair (i, i + half): (u, v) -> (u cos - v sin, v cos + u sin)
                     const bool lo = d < half;
                     const float2 cs = a.rot_tab[(size_t)(pos + t0 + t) * half + (lo ? d : d - half)];
@@ -146,6 +152,20 @@ __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
             vs[t][j] = j0 + j < a.VD ? a.p[(size_t)(t0 + t) * a.ld + a.v0 + h * a.VD + j0 + j] : 0.0f;
         }
         __syncthreads();
+        if (a.mode == 1u) {          // the first pass of a long portion only builds states
+            for (uint32_t t = 0; t < nt; t++) {
+                float v[kRetCpw];
+#pragma unroll
+                for (uint32_t i = 0; i < kRetCpw; i++) v[i] = vs[t][warp * kRetCpw + i];
+#pragma unroll
+                for (int c = 0; c < DCH; c++) {
+                    const float kd = ks[t][lane + 32 * c];
+#pragma unroll
+                    for (uint32_t i = 0; i < kRetCpw; i++) S[i][c] = fmaf(g, S[i][c], kd * v[i]);
+                }
+            }
+            continue;
+        }
         for (uint32_t t = 0; t < nt; t++) {
             float acc[kRetCpw], v[kRetCpw];
 #pragma unroll
@@ -156,18 +176,32 @@ __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
 #pragma unroll
                 for (uint32_t i = 0; i < kRetCpw; i++) { S[i][c] = fmaf(g, S[i][c], kd * v[i]); acc[i] = fmaf(S[i][c], qd, acc[i]); }
             }
+            float *orow = a.o + (size_t)(t0 + t) * a.H * a.VD + h * a.VD + jw;
+            if (kRetCpw == 4) {
+                // four sums over the warp with six shuffles: halves of the warp trade two columns, quarters one, then eight lanes add up;
+                // lanes 0, 8, 16, 24 end with columns 0, 1, 2, 3
+                const bool h16 = lane & 16u, h8 = lane & 8u;
+                float k0 = (h16 ? acc[2] : acc[0]) + __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[2], 16);
+                float k1 = (h16 ? acc[3] : acc[1]) + __shfl_xor_sync(0xffffffffu, h16 ? acc[1] : acc[3], 16);
+                float k = (h8 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
+                k += __shfl_xor_sync(0xffffffffu, k, 4); k += __shfl_xor_sync(0xffffffffu, k, 2); k += __shfl_xor_sync(0xffffffffu, k, 1);
+                const uint32_t col = lane >> 3;
+                if ((lane & 7u) == 0 && jw + col < a.VD) orow[col] = k;
+            } else {
 #pragma unroll
-            for (uint32_t i = 0; i < kRetCpw; i++) acc[i] = warp_sum(acc[i]);
-            float mine = acc[0];
+                for (uint32_t i = 0; i < kRetCpw; i++) acc[i] = warp_sum(acc[i]);
+                float mine = acc[0];
 #pragma unroll
-            for (uint32_t i = 1; i < kRetCpw; i++) if (lane == i) mine = acc[i];
-            if (lane < kRetCpw && jw + lane < a.VD) a.o[(size_t)(t0 + t) * a.H * a.VD + h * a.VD + jw + lane] = mine;
+                for (uint32_t i = 1; i < kRetCpw; i++) if (lane == i) mine = acc[i];
+                if (lane < kRetCpw && jw + lane < a.VD) orow[lane] = mine;
+            }
         }
     }
+    if (a.mode == 2u) return;
 #pragma unroll
     for (uint32_t i = 0; i < kRetCpw; i++)
 #pragma unroll
-        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; if (jw + i < a.VD && d < a.D) a.S[((size_t)h * a.VD + jw + i) * a.D + d] = S[i][c]; }
+        for (int c = 0; c < DCH; c++) { const uint32_t d = lane + 32u * c; if (jw + i < a.VD && d < a.D) Sio[((size_t)h * a.VD + jw + i) * a.D + d] = S[i][c]; }
     if (!a.finish) return;
     __shared__ uint32_t last_s;
     __threadfence();
@@ -188,6 +222,31 @@ __global__ void __launch_bounds__(256) k_retention_scan(const RetentionArgs a) {
         const float rinv = 1.0f / sqrtf(s / (float)a.VD + a.eps);
         float *out = a.out + ((size_t)t * a.H + h) * a.VD;
         for (uint32_t i = lane; i < a.VD; i += 32u) out[i] = __ldcg(o + i) * rinv * siluf_(gp[i]);
+    }
+}
+
+// Between the two passes of a long portion: seg_S[s] holds what segment s built from zero; it becomes the state segment s starts
+// from, S_s = decay^len(s-1) S_(s-1) + built(s-1), S_0 = the slot's state, which in turn becomes the state after the last segment.
+struct RetChainArgs { float *S; float *seg_S; const float *decay; uint32_t H, D, VD, T, seg_len, nseg; };      // nseg <= 8
+__global__ void __launch_bounds__(256) k_retention_chain(const RetChainArgs a) {
+    pdl_enter();
+    const uint32_t per = a.VD * a.D, h = blockIdx.y;          // grid = (blocks over a head's state, heads)
+    const size_t total = (size_t)per * a.H;
+    const float g = a.decay[h], lg = log2f(g);
+    for (uint32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < per; j += gridDim.x * blockDim.x) {
+        const size_t i = (size_t)h * per + j;
+        float built[8];
+#pragma unroll
+        for (uint32_t sg = 0; sg < 8; sg++) built[sg] = sg < a.nseg ? a.seg_S[(size_t)sg * total + i] : 0.0f;
+        float s = a.S[i];
+#pragma unroll
+        for (uint32_t sg = 0; sg < 8; sg++) {
+            if (sg >= a.nseg) break;
+            const uint32_t len = min(a.T, (sg + 1u) * a.seg_len) - sg * a.seg_len;
+            a.seg_S[(size_t)sg * total + i] = s;
+            s = fmaf(exp2f((float)len * lg), s, built[sg]);          // decay^len
+        }
+        a.S[i] = s;
     }
 }
 
@@ -557,6 +616,7 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     for (int k = 0; k < 4; k++) { const uint32_t n = g + LG * k; Av[k] = (live && n < a.N) ? a.A[(size_t)c * a.N + n] : 0.0f; }
     {
         float zs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
         for (uint32_t t = t0; t < t1; t++) {
             const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, dx = live ? dtc * a.x[(size_t)t * a.C + c] : 0.0f;
             const float *row = a.bc + (size_t)t * a.ldb;
@@ -585,6 +645,7 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
 #pragma unroll
     for (int k = 0; k < 4; k++) S[k] = (live && g + LG * k < a.N) ? P[seg][x][k] : 0.0f;
     const float Dc = live ? a.Dv[c] : 0.0f;
+#pragma unroll 4
     for (uint32_t t = t0; t < t1; t++) {
         const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
         const float *row = a.bc + (size_t)t * a.ldb;
