@@ -426,7 +426,15 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
         for (uint32_t i = 0; i < kGemvMaxM; i++)
             if (i < rows) {
                 float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
-                for (uint32_t k = threadIdx.x; k < a.K; k += blockDim.x) { const float v = ap[i][k], v2 = v * v, v3 = v2 * v; s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6); }
+                const uint32_t k4 = vec ? a.K & ~3u : 0u;          // 16-byte loads where the row allows them
+#pragma unroll 4
+                for (uint32_t k = threadIdx.x * 4u; k < k4; k += blockDim.x * 4u) {
+                    const float4 q = *reinterpret_cast<const float4 *>(ap[i] + k);
+                    const float w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const float v2 = w[j] * w[j], v3 = v2 * w[j]; s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6); }
+                }
+                for (uint32_t k = k4 + threadIdx.x; k < a.K; k += blockDim.x) { const float v = ap[i][k], v2 = v * v, v3 = v2 * v; s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6); }
                 s2 = block_sum(s2, red); s4 = block_sum(s4, red); s6 = block_sum(s6, red);
                 pc[i].r1 = a.a_poly[0] / sqrtf(s2 / (float)a.K + a.a_eps); pc[i].r2 = a.a_poly[1] / sqrtf(s4 / (float)a.K + a.a_eps);
                 pc[i].r3 = a.a_poly[2] / sqrtf(s6 / (float)a.K + a.a_eps); pc[i].e = a.a_poly[3];

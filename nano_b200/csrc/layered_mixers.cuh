@@ -610,6 +610,9 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     __shared__ float P[32][32][4], Q[32][32][4];
     const uint32_t x = threadIdx.x, seg = threadIdx.y, nseg = blockDim.y, gid = blockIdx.x * 32u + x, c = gid / LG, g = gid % LG;
     const uint32_t Ls = (a.T + nseg - 1u) / nseg, t0 = min(a.T, seg * Ls), t1 = min(a.T, t0 + Ls);
+    // inputs and output never overlap: with that said, the loads of the unrolled steps can all be issued before the first store
+    const float *__restrict__ dtp = a.dt, *__restrict__ xp = a.x, *__restrict__ bcp = a.bc, *__restrict__ zp = a.z;
+    float *__restrict__ yp = a.y;
     const bool live = c < a.C;
     float Av[4];
 #pragma unroll
@@ -618,8 +621,8 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
         float zs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
         for (uint32_t t = t0; t < t1; t++) {
-            const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, dx = live ? dtc * a.x[(size_t)t * a.C + c] : 0.0f;
-            const float *row = a.bc + (size_t)t * a.ldb;
+            const float dtc = live ? dtp[(size_t)t * a.C + c] : 0.0f, dx = live ? dtc * xp[(size_t)t * a.C + c] : 0.0f;
+            const float *__restrict__ row = bcp + (size_t)t * a.ldb;
 #pragma unroll
             for (int k = 0; k < 4; k++) {
                 const uint32_t n = g + LG * k;
@@ -647,8 +650,8 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     const float Dc = live ? a.Dv[c] : 0.0f;
 #pragma unroll 4
     for (uint32_t t = t0; t < t1; t++) {
-        const float dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f, xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
-        const float *row = a.bc + (size_t)t * a.ldb;
+        const float dtc = live ? dtp[(size_t)t * a.C + c] : 0.0f, xv = live ? xp[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
+        const float *__restrict__ row = bcp + (size_t)t * a.ldb;
         float acc = 0.0f;
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -657,7 +660,7 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
         }
 #pragma unroll
         for (int off = LG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (live && g == 0) a.y[(size_t)t * a.C + c] = (acc + Dc * xv) * siluf_(a.z[(size_t)t * a.ldz + c]);
+        if (live && g == 0) yp[(size_t)t * a.C + c] = (acc + Dc * xv) * siluf_(zp[(size_t)t * a.ldz + c]);
     }
 }
 
