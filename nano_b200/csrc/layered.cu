@@ -17,9 +17,10 @@
 //   loader         config -> layer table; tensors -> HBM in the compute type (bf16 as stored, or widened to fp32 with NB200_FLAG_F32),
 //                  fused where one product serves two projections ([y | x] of the recurrent block, [query latent | kv latent],
 //                  [recurrence gate | input gate] blocks, experts stacked), W_uk transposed per head so queries can be absorbed
-//   state manager  sequences = {cache pages, one state slot}.  Pages of kPage tokens come from a LIFO free list and hold the latent
-//                  rows of EVERY attention layer run; a slot holds, per layer run, the previous mixer input (token shift) and, for a
-//                  recurrent run, the fp32 state and the convolution tail.  Slots are zeroed when a sequence opens.
+//   state manager  sequences = {cache pages, one state slot}.  Pages of kPage tokens come from a LIFO free list and hold the rows
+//                  of EVERY attention layer run (latents, or key/value rows of a window attention); a slot holds, per layer run,
+//                  what the run carries from token to token: the previous mixer input (token shift), fp32 recurrent states
+//                  (rglru, retention, selective scan) and convolution tails.  Slots are zeroed when a sequence opens.
 //   step           a portion of n tokens is cut into chunks of <= chunk_cap tokens; each chunk runs every layer run with the prefill
 //                  kernels (n > kGemvMaxM) or the decode kernels; logits only where asked
 //   generation     the C-ABI's forward / next_greedy / next_sampled / decode_greedy on one implicit sequence; the greedy loop feeds

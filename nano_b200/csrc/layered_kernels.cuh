@@ -21,6 +21,9 @@
 //                        (both in one block, short portions),
 //                        k_combine (weighted sum in choice order + shared expert + mixer output -> residual)
 //
+// More mechanisms (position table, sandwich norms, rotary positions, retention, window attention, selective scan, PolyNorm) live in
+// layered_mixers.cuh under the same rules.
+//
 // What is fp32 here regardless of the weight type: the residual stream, every norm, router logits, attention scores / weights /
 // accumulators, gates, decays and the recurrent state.  bf16 enters only as a matrix-product operand.
 #pragma once

@@ -8,13 +8,16 @@
 //   rotary positions     k_rope ("rotate half" pairs over the first `dims` coordinates of each head, angles from a table built in
 //                        double precision, optional scale on k after the rotation)
 //   retention            k_retention_scan (linear attention with a fixed decay per head, no softmax, no denominator:
-//                        S <- decay S + k v^T, o = S^T q; fp32 state [head][value column][key coordinate]), k_retention_out
-//                        (per-head unit RMS of o times silu(gate)), k_retention_step (both, with the rotation, for short portions)
+//                        S <- decay S + k v^T, o = S^T q; fp32 state [head][value column][key coordinate]; long portions as time
+//                        segments side by side with k_retention_chain between the two passes; short portions rotate q and k while
+//                        staging and finish the head's output in the last block), k_retention_out (per-head unit RMS of o times
+//                        silu(gate))
 //   window attention     k_qk_prepare (unit-RMS q and k per head, score scale and temperature folded into q, convolved k and its
 //                        inverse RMS into the paged cache: the cached row is value AND, times that factor, key), k_window_attn
 //                        (grouped-query softmax attention in a sliding window: soft cap, per-head distance slopes, scores mixed
 //                        across heads before the softmax, sigmoid output gate)
-//   selective scan       k_selective_scan (Mamba: S <- exp(dt A) S + dt x B, y = S C + D x, times silu(z); fp32 state [channel][n])
+//   selective scan       k_selective_scan (Mamba: S <- exp(dt A) S + dt x B, y = S C + D x, times silu(z); fp32 state [channel][n]),
+//                        k_selective_scan_par (the same, parallel over time segments)
 //   feed-forward         k_polynorm (a N(z) + b N(z^2) + c N(z^3) + e over the feed-forward width, N = unit RMS)
 #pragma once
 #include "layered_kernels.cuh"
