@@ -1187,8 +1187,11 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         std::vector<uint32_t> owner(NL);
         for (uint32_t i = 0; i < NL; i++) {
             owner[i] = i;
-            if (layers->arr[i].present("weights_of") && (!u32_of(&layers->arr[i], "weights_of", &owner[i]) || owner[i] >= NL || layers->arr[owner[i]].present("weights_of")))
-                return fail(NB200_EINVAL, "layer %u: weights_of must name a layer with weights of its own", i);
+            for (uint32_t hops = 0; layers->arr[owner[i]].present("weights_of"); hops++) {          // a named layer may itself name another
+                uint32_t j = 0;
+                if (!u32_of(&layers->arr[owner[i]], "weights_of", &j) || j >= NL || hops > NL) return fail(NB200_EINVAL, "layer %u: weights_of must lead to a layer with weights of its own", i);
+                owner[i] = j;
+            }
         }
         for (uint32_t i = 0; i < NL; i++) {
             Run q; q.layer = owner[i]; e->runs.push_back(q);

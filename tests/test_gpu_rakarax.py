@@ -302,6 +302,12 @@ def test_greedy_generation(tmp_path):
             ids2[pos + 1] = nxt
     assert np.array_equal(ids[:total], ids2[:total])
     eng.close()
+    # the generation command on the same folder
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "nano_b200.generate", "--model", str(tmp_path / "m"), "--prompt-ids", ",".join(str(int(x)) for x in prompt),
+                        "--max-new", str(total - 17), "--dtype", "float32"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(x) for x in p.stdout.split()] == [int(x) for x in ids[:total]]
 
 
 def test_position_limit_is_refused(tmp_path):
