@@ -543,8 +543,8 @@ __global__ void __launch_bounds__(512) k_window_attn(const WinAttnArgs a) {
     }
 }
 
-// Selective scan (Mamba), token by token.  A group of LG lanes owns channel c; lane g of the group holds the states n = g, g + LG, ...
-// (at most 4 per lane).  Per token:  S[c][n] <- exp(dt_c A[c][n]) S[c][n] + (dt_c x_c) B_n,  y_c = sum_n S[c][n] C_n + D_c x_c,
+// Selective scan (Mamba), token by token.  A group of LG lanes owns channel c; lane g of the group holds the states n = 4g .. 4g + 3
+// (their B and C are one 16-byte load each where the row layout allows).  Per token:  S[c][n] <- exp(dt_c A[c][n]) S[c][n] + (dt_c x_c) B_n,  y_c = sum_n S[c][n] C_n + D_c x_c,
 // out = y_c silu(z_c).  dt [T][C] is the step size after its softplus, x [T][C] the convolved, activated input, B and C sit in the
 // rows of bc at columns b0 and c0, A = -exp(A_log) [C][N].
 // exp(z) S + b for z <= 0.  A slowly decaying state takes thousands of these steps, and the error of expf (two units in the last
@@ -559,6 +559,14 @@ __device__ __forceinline__ float decay_drive(float z, float S, float b) {
 }
 // With dt_w (fp32 [C][R], short portions) the step size is made here: dt_c = softplus(dt_w[c] . bc[t][0..R) + dt_b[c]); round_a rounds
 // that operand to bf16 first, as a tensor-core product of the same numbers would.
+// four consecutive values row[n0 .. n0 + 4) of a [.., N] row (zeros past N): one 16-byte load where the layout allows it
+__device__ __forceinline__ void load4(const float *__restrict__ p, uint32_t n0, uint32_t N, bool vec, float (&v)[4]) {
+    if (vec && n0 + 4u <= N) { const float4 q = *reinterpret_cast<const float4 *>(p + n0); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+    else {
+#pragma unroll
+        for (uint32_t k = 0; k < 4; k++) v[k] = n0 + k < N ? p[n0 + k] : 0.0f;
+    }
+}
 struct SelScanArgs { const float *dt; const float *x; const float *bc; uint32_t ldb, b0, c0; const float *A, *Dv; const float *z; uint32_t ldz;
                      float *S; float *y; uint32_t T, C, N; const float *dt_w, *dt_b; uint32_t R, round_a; };
 template <int LG>
@@ -566,10 +574,11 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
     pdl_enter();
     const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x, c = gid / LG, g = gid % LG;
     const bool live = c < a.C;          // dead lanes keep running: the group sums are warp shuffles
+    const bool vec4 = ((a.b0 | a.c0 | a.ldb) & 3u) == 0 && (reinterpret_cast<uintptr_t>(a.bc) & 15u) == 0;
     float S[4], Av[4];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-        const uint32_t n = g + LG * k;
+        const uint32_t n = g * 4u + k;
         const bool ok = live && n < a.N;
         S[k] = ok ? a.S[(size_t)c * a.N + n] : 0.0f;
         Av[k] = ok ? a.A[(size_t)c * a.N + n] : 0.0f;
@@ -586,13 +595,13 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
             dtc = live ? softplusf_(s + a.dt_b[c]) : 0.0f;
         } else dtc = live ? a.dt[(size_t)t * a.C + c] : 0.0f;
         const float xv = live ? a.x[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
-        float acc = 0.0f;
+        float acc = 0.0f, Bv[4], Cv[4];
+        load4(row + a.b0, g * 4u, a.N, vec4, Bv); load4(row + a.c0, g * 4u, a.N, vec4, Cv);
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            const uint32_t n = g + LG * k;
-            if (n < a.N) {
-                S[k] = decay_drive(dtc * Av[k], S[k], dx * row[a.b0 + n]);
-                acc = fmaf(S[k], row[a.c0 + n], acc);
+            if (g * 4u + k < a.N) {
+                S[k] = decay_drive(dtc * Av[k], S[k], dx * Bv[k]);
+                acc = fmaf(S[k], Cv[k], acc);
             }
         }
 #pragma unroll
@@ -601,7 +610,7 @@ __global__ void __launch_bounds__(256) k_selective_scan(const SelScanArgs a) {
     }
     if (live)
 #pragma unroll
-        for (int k = 0; k < 4; k++) { const uint32_t n = g + LG * k; if (n < a.N) a.S[(size_t)c * a.N + n] = S[k]; }
+        for (int k = 0; k < 4; k++) { const uint32_t n = g * 4u + k; if (n < a.N) a.S[(size_t)c * a.N + n] = S[k]; }
 }
 
 // The same scan for long portions, parallel over time: blockDim = (32, segments).  A thread first composes its time segment's
@@ -617,20 +626,20 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     const float *__restrict__ dtp = a.dt, *__restrict__ xp = a.x, *__restrict__ bcp = a.bc, *__restrict__ zp = a.z;
     float *__restrict__ yp = a.y;
     const bool live = c < a.C;
+    const bool vec4 = ((a.b0 | a.c0 | a.ldb) & 3u) == 0 && (reinterpret_cast<uintptr_t>(a.bc) & 15u) == 0;
     float Av[4];
 #pragma unroll
-    for (int k = 0; k < 4; k++) { const uint32_t n = g + LG * k; Av[k] = (live && n < a.N) ? a.A[(size_t)c * a.N + n] : 0.0f; }
+    for (int k = 0; k < 4; k++) { const uint32_t n = g * 4u + k; Av[k] = (live && n < a.N) ? a.A[(size_t)c * a.N + n] : 0.0f; }
     {
         float zs[4] = {0.0f, 0.0f, 0.0f, 0.0f}, q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
         for (uint32_t t = t0; t < t1; t++) {
             const float dtc = live ? dtp[(size_t)t * a.C + c] : 0.0f, dx = live ? dtc * xp[(size_t)t * a.C + c] : 0.0f;
-            const float *__restrict__ row = bcp + (size_t)t * a.ldb;
+            float Bv[4];
+            load4(bcp + (size_t)t * a.ldb + a.b0, g * 4u, a.N, vec4, Bv);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const uint32_t n = g + LG * k;
-                if (n < a.N) { const float z = dtc * Av[k]; q[k] = decay_drive(z, q[k], dx * row[a.b0 + n]); zs[k] += z; }
-            }
+            for (int k = 0; k < 4; k++)
+                if (g * 4u + k < a.N) { const float z = dtc * Av[k]; q[k] = decay_drive(z, q[k], dx * Bv[k]); zs[k] += z; }
         }
 #pragma unroll
         for (int k = 0; k < 4; k++) { P[seg][x][k] = expf(zs[k]); Q[seg][x][k] = q[k]; }
@@ -639,7 +648,7 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     if (seg == 0 && live) {
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            const uint32_t n = g + LG * k;
+            const uint32_t n = g * 4u + k;
             if (n >= a.N) continue;
             float s = a.S[(size_t)c * a.N + n];
             for (uint32_t sg = 0; sg < nseg; sg++) { const float pg = P[sg][x][k], qg = Q[sg][x][k]; P[sg][x][k] = s; s = fmaf(pg, s, qg); }
@@ -649,18 +658,17 @@ __global__ void __launch_bounds__(1024) k_selective_scan_par(const SelScanArgs a
     __syncthreads();
     float S[4];
 #pragma unroll
-    for (int k = 0; k < 4; k++) S[k] = (live && g + LG * k < a.N) ? P[seg][x][k] : 0.0f;
+    for (int k = 0; k < 4; k++) S[k] = (live && g * 4u + k < a.N) ? P[seg][x][k] : 0.0f;
     const float Dc = live ? a.Dv[c] : 0.0f;
 #pragma unroll 4
     for (uint32_t t = t0; t < t1; t++) {
         const float dtc = live ? dtp[(size_t)t * a.C + c] : 0.0f, xv = live ? xp[(size_t)t * a.C + c] : 0.0f, dx = dtc * xv;
         const float *__restrict__ row = bcp + (size_t)t * a.ldb;
-        float acc = 0.0f;
+        float acc = 0.0f, Bv[4], Cv[4];
+        load4(row + a.b0, g * 4u, a.N, vec4, Bv); load4(row + a.c0, g * 4u, a.N, vec4, Cv);
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t n = g + LG * k;
-            if (n < a.N) { S[k] = decay_drive(dtc * Av[k], S[k], dx * row[a.b0 + n]); acc = fmaf(S[k], row[a.c0 + n], acc); }
-        }
+        for (int k = 0; k < 4; k++)
+            if (g * 4u + k < a.N) { S[k] = decay_drive(dtc * Av[k], S[k], dx * Bv[k]); acc = fmaf(S[k], Cv[k], acc); }
 #pragma unroll
         for (int off = LG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (live && g == 0) yp[(size_t)t * a.C + c] = (acc + Dc * xv) * siluf_(zp[(size_t)t * a.ldz + c]);
