@@ -611,9 +611,20 @@ int win_attn_launch(LayeredEngine *e, const Layer &L, const WinAttnArgs &a) {
     return win_attn_launch_v<8>(e, a, qt, hs);
 }
 
+constexpr size_t kSelStageMax = 160 * 1024;      // dynamic shared memory the time-parallel scan may stage its inputs in (32 KB of maps are static)
+template <int LG>
+int sel_scan_optin() {
+    CK(cudaFuncSetAttribute((const void *)k_selective_scan_par<LG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSelStageMax));
+    return 0;
+}
 template <int LG>
 int sel_scan_launch(LayeredEngine *e, const SelScanArgs &a) {
-    if (a.T > 32) return launch<SelScanArgs>(e, k_selective_scan_par<LG>, dim3(((size_t)a.C * LG + 31u) / 32u), dim3(32, a.T >= 256 ? 32 : 8), 0, a);
+    if (a.T > 32) {
+        const dim3 grid(((size_t)a.C * LG + 31u) / 32u), block(32, a.T >= 256 ? 32 : 8);
+        const size_t stage = sel_scan_stage_bytes(a.T, LG);
+        if (stage <= kSelStageMax) return launch<SelScanArgs>(e, k_selective_scan_par<LG, true>, grid, block, stage, a);
+        return launch<SelScanArgs>(e, k_selective_scan_par<LG, false>, grid, block, 0, a);
+    }
     return launch<SelScanArgs>(e, k_selective_scan<LG>, dim3(((size_t)a.C * LG + 255u) / 256u), dim3(256), 0, a);
 }
 
@@ -1287,6 +1298,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         }
         if (L.ff_kind == FF_DENSE_POLY) sF = std::max(sF, L.ff);
     }
+    if (sQK && ((r = sel_scan_optin<1>()) || (r = sel_scan_optin<2>()) || (r = sel_scan_optin<4>()) || (r = sel_scan_optin<8>()) || (r = sel_scan_optin<16>()) || (r = sel_scan_optin<32>()))) return r;
     if (win_smem[0] > 48 * 1024 && (r = win_attn_optin_v<1>((int)win_smem[0]))) return r;
     if (win_smem[1] > 48 * 1024 && (r = win_attn_optin_v<2>((int)win_smem[1]))) return r;
     if (win_smem[2] > 48 * 1024 && (r = win_attn_optin_v<4>((int)win_smem[2]))) return r;
